@@ -85,6 +85,7 @@ class CacheGroup:
     pool: Optional[PagePool]                       # None for groups that keep no keys/values
     kv: Dict[int, torch.Tensor] = field(default_factory=dict)
     state: Dict[int, torch.Tensor] = field(default_factory=dict)
+    states: Dict[int, Dict[str, torch.Tensor]] = field(default_factory=dict)   # entry -> named float32 states
 
     @property
     def paged(self) -> bool:
@@ -92,7 +93,7 @@ class CacheGroup:
 
     def page_bytes(self, element_size: int) -> int:
         n = self.need
-        return 2 * n.kv_heads * n.head_dim * self.page_size * element_size * len(self.entries)
+        return n.kv_heads * (n.head_dim + n.v_dim) * self.page_size * element_size * len(self.entries)
 
 
 class _Table:
@@ -153,7 +154,7 @@ class CacheManager:
             key = need.group_key()
             if key not in by_key:
                 by_key[key] = len(self.groups)
-                pool = PagePool(num_pages) if need.kind in ("full", "window") else None
+                pool = PagePool(num_pages) if need.kind in ("full", "window", "chunk") else None
                 self.groups.append(CacheGroup(need, [], page_size, pool))
             g = by_key[key]
             self.groups[g].entries.append(e)
@@ -162,9 +163,16 @@ class CacheManager:
             for grp in self.groups:
                 n = grp.need
                 for e in grp.entries:
-                    if grp.paged:
+                    if grp.paged and n.v_dim == n.head_dim:
                         grp.kv[e] = torch.zeros((num_pages, 2, n.kv_heads, page_size, n.head_dim),
                                                 dtype=dtype, device=self.device)
+                    elif grp.paged:     # a page holds its keys, then its values
+                        grp.kv[e] = torch.zeros((num_pages, n.kv_heads * page_size * (n.head_dim + n.v_dim)),
+                                                dtype=dtype, device=self.device)
+                    if n.states:
+                        # Not cleared when a slot is taken again: a mixer starts from zero at position 0.
+                        grp.states[e] = {name: torch.zeros((max_requests, *shape), dtype=torch.float32, device=self.device)
+                                         for name, shape in n.states}
                     if n.state_shape is not None:
                         grp.state[e] = torch.zeros((max_requests, *n.state_shape),
                                                    dtype=n.state_dtype or torch.float32, device=self.device)
@@ -201,9 +209,12 @@ class CacheManager:
 
     def _first_needed_block(self, grp: CacheGroup, next_pos: int) -> int:
         """Blocks below this index hold no key that a query at ``next_pos`` or later can see."""
-        if grp.need.kind != "window":
+        if grp.need.kind == "chunk":
+            first_key = next_pos // grp.need.window * grp.need.window
+        elif grp.need.kind == "window":
+            first_key = max(0, next_pos - grp.need.window + 1)
+        else:
             return 0
-        first_key = max(0, next_pos - grp.need.window + 1)
         return first_key // self.page_size
 
     def pages_needed(self, req: Optional[Hashable], new_tokens: int, have_tokens: Optional[int] = None) -> Dict[int, int]:
@@ -221,7 +232,7 @@ class CacheManager:
                 continue
             held = len(r.tables[gi]) if r else -(-have // self.page_size)
             need = total_blocks - held
-            if r is not None and grp.need.kind == "window":
+            if r is not None and grp.need.kind in ("window", "chunk"):
                 need -= r.tables[gi].held_below(self._first_needed_block(grp, have))
             out[gi] = need
         return out

@@ -1,4 +1,5 @@
 from .llama import ConfigError, LlamaConfig, RopeScaling  # noqa: F401
 from .engine import EngineConfig  # noqa: F401
+from .tibepel import TibepelConfig  # noqa: F401
 from .registry import (known_architectures, read_config_json, register_architecture,  # noqa: F401
                        resolve_architecture)

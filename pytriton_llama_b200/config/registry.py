@@ -1,5 +1,5 @@
-"""One registry from an architecture's name (config.json ``architectures[0]``) to its typed
-configuration and its model description.
+"""One registry from an architecture's name (config.json ``architectures[0]``, or the single name
+under ``architecture``) to its typed configuration and its model description.
 
 lite_llama branches on ``model_type`` in two if/elif chains
 (lite_llama/executor/model_executor.py:141-153,170-181); here both the configuration class and
@@ -32,10 +32,10 @@ def known_architectures():
 
 
 def resolve_architecture(config: Dict[str, Any]) -> Architecture:
-    archs = config.get("architectures")
+    archs = config.get("architectures") or config.get("architecture")
     if not archs:
-        raise KeyError(f"config.json has no 'architectures'; known: {known_architectures()}")
-    name = archs[0]
+        raise KeyError(f"config.json has neither 'architectures' nor 'architecture'; known: {known_architectures()}")
+    name = archs if isinstance(archs, str) else archs[0]
     if name not in _ARCHITECTURES:
         raise KeyError(f"architecture {name!r} is not registered; known: {known_architectures()}")
     return _ARCHITECTURES[name]
@@ -52,6 +52,9 @@ def _register_builtin() -> None:
     from .llama import LlamaConfig
     from ..models.llama import llama_spec
     register_architecture("LlamaForCausalLM", LlamaConfig.from_dict, llama_spec)
+    from .tibepel import TibepelConfig
+    from ..models.tibepel import tibepel_spec
+    register_architecture("Tibepel", TibepelConfig.from_dict, tibepel_spec)
 
 
 _register_builtin()

@@ -36,7 +36,7 @@ __global__ void embed_gather_kernel(T* __restrict__ out, const T* __restrict__ t
 
 // ------------------------------------------------------------------ add + RMSNorm
 // For output row m (input row r = rows ? rows[m] : m):
-//   s = (residual_in ? residual_in[r] : 0) + (x ? x[r] : 0)          in float32
+//   s = (residual_in ? residual_in[r] : 0) + (x ? x[r] : 0) + (bias ? bias : 0)     in float32
 //   residual_out[m] = s                                              (if residual_out)
 //   y[m] = s * rsqrt(mean(s^2) + eps) * w                            rounded once to T
 // The row is kept in shared memory between the two passes.
@@ -44,7 +44,7 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residual_out,
                                    const float* __restrict__ residual_in, const T* __restrict__ x,
                                    const float* __restrict__ w, const int* __restrict__ rows,
-                                   int hidden, float eps, int vec_ok) {
+                                   int hidden, float eps, int vec_ok, const float* __restrict__ bias) {
   extern __shared__ float row[];
   __shared__ float red[33];
   pdl_wait();
@@ -72,8 +72,12 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
           s.z += __bfloat162float(b.x); s.w += __bfloat162float(b.y);
         }
       }
+      if (bias) {
+        const float4 v = *reinterpret_cast<const float4*>(bias + i);
+        s.x += v.x; s.y += v.y; s.z += v.z; s.w += v.w;
+      }
       *reinterpret_cast<float4*>(row + i) = s;
-      if (rout && (xin || rout != rin)) *reinterpret_cast<float4*>(rout + i) = s;   // unchanged rows are not rewritten
+      if (rout && (xin || bias || rout != rin)) *reinterpret_cast<float4*>(rout + i) = s;   // unchanged rows are not rewritten
       ss += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
     }
     ss = block_sum(ss, red);
@@ -95,6 +99,7 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     float s = rin ? rin[i] : 0.f;
     if (xin) s += to_f32(xin[i]);
+    if (bias) s += bias[i];
     row[i] = s;
     ss += s * s;
   }
@@ -102,7 +107,7 @@ __global__ void add_rmsnorm_kernel(T* __restrict__ y, float* __restrict__ residu
   const float rrms = 1.0f / sqrtf(ss / (float)hidden + eps);
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
     const float s = row[i];
-    if (rout && (xin || rout != rin)) rout[i] = s;
+    if (rout && (xin || bias || rout != rin)) rout[i] = s;
     yo[i] = from_f32<T>(s * rrms * w[i]);
   }
 }
@@ -243,7 +248,7 @@ int embed_gather(void* out, const void* table, const int* ids, int tokens, int h
 
 template <typename T>
 int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const void* x, const float* w,
-                const int* rows, int out_rows, int hidden, float eps, void* stream) {
+                const int* rows, int out_rows, int hidden, float eps, void* stream, const float* bias = nullptr) {
   PTL_REQUIRE(out_rows >= 0 && hidden > 0, "add_rmsnorm: bad sizes rows=%d hidden=%d", out_rows, hidden);
   PTL_REQUIRE(residual_in || x, "add_rmsnorm: needs a residual or an input");
   PTL_REQUIRE(eps > 0.f, "add_rmsnorm: eps must be positive");
@@ -254,9 +259,10 @@ int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const vo
   if (smem > 48 * 1024)
     if (int rc = raise_shared_memory("add_rmsnorm", add_rmsnorm_kernel<T>, 200 * 1024, raised)) return rc;
   const int vec_ok = hidden % 4 == 0 && aligned16(y) && aligned16(w) && (!x || aligned16(x)) &&
-                     (!residual_in || aligned16(residual_in)) && (!residual_out || aligned16(residual_out));
+                     (!residual_in || aligned16(residual_in)) && (!residual_out || aligned16(residual_out)) &&
+                     (!bias || aligned16(bias));
   // many rows of a common width: a warp per row
-  if (vec_ok && out_rows >= 256 && hidden % 512 == 0 && hidden <= 4096) {
+  if (vec_ok && !bias && out_rows >= 256 && hidden % 512 == 0 && hidden <= 4096) {
     const dim3 grid((out_rows + 7) / 8), block(256);
 #define PTL_NORM_ROWS(N4) launch_kernel("add_rmsnorm", add_rmsnorm_warp_kernel<T, N4>, grid, block, 0, as_stream(stream), \
                                         (T*)y, residual_out, residual_in, (const T*)x, w, rows, out_rows, eps)
@@ -274,7 +280,7 @@ int add_rmsnorm(void* y, float* residual_out, const float* residual_in, const vo
   }
   int threads = hidden >= 8192 ? 1024 : (hidden >= 2048 ? 512 : (hidden >= 1024 ? 256 : 128));
   return launch_kernel("add_rmsnorm", add_rmsnorm_kernel<T>, dim3(out_rows), dim3(threads), smem, as_stream(stream),
-                       (T*)y, residual_out, residual_in, (const T*)x, w, rows, hidden, eps, vec_ok);
+                       (T*)y, residual_out, residual_in, (const T*)x, w, rows, hidden, eps, vec_ok, bias);
 }
 
 template <typename T>
@@ -350,6 +356,13 @@ PTL_EXPORT int ptl_add_rmsnorm_f32(void* y, float* residual_out, const float* re
 }
 PTL_EXPORT int ptl_add_rmsnorm_bf16(void* y, float* residual_out, const float* residual_in, const void* x, const float* w, const int* rows, int out_rows, int hidden, float eps, void* stream) {
   return ptl::add_rmsnorm<__nv_bfloat16>(y, residual_out, residual_in, x, w, rows, out_rows, hidden, eps, stream);
+}
+// The same with the bias of the projection that made x (float32 [hidden]) added into the sum.
+PTL_EXPORT int ptl_add_bias_rmsnorm_f32(void* y, float* residual_out, const float* residual_in, const void* x, const float* bias, const float* w, const int* rows, int out_rows, int hidden, float eps, void* stream) {
+  return ptl::add_rmsnorm<float>(y, residual_out, residual_in, x, w, rows, out_rows, hidden, eps, stream, bias);
+}
+PTL_EXPORT int ptl_add_bias_rmsnorm_bf16(void* y, float* residual_out, const float* residual_in, const void* x, const float* bias, const float* w, const int* rows, int out_rows, int hidden, float eps, void* stream) {
+  return ptl::add_rmsnorm<__nv_bfloat16>(y, residual_out, residual_in, x, w, rows, out_rows, hidden, eps, stream, bias);
 }
 PTL_EXPORT int ptl_silu_mul_f32(void* out, const void* gu, int tokens, int inter, void* stream) {
   return ptl::silu_mul<float>(out, gu, tokens, inter, stream);

@@ -1,0 +1,347 @@
+// Kernels of the mixers that carry a per-request state of fixed size from step to step: the short
+// causal convolution, the selective scan, the gated delta rule, and the per-head norm with an output
+// gate.  States are float32 arrays [slots, ...]; a request's slot is state_slot[r], and a request
+// whose first token of the step has position 0 starts from zeros whatever its slot holds.  A step's
+// tokens lie request after request: request r owns rows q_start[r] .. q_start[r + 1] - 1.
+// T is the element type of the projections' results; everything inside is float32.
+#include "common.cuh"
+
+namespace ptl {
+
+__device__ __forceinline__ float softplus_f32(float x) { return x > 20.f ? x : log1pf(expf(x)); }
+__device__ __forceinline__ float silu_f32(float x) { return x / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------ causal convolution per channel
+// y[t, c] = act(b[c] + sum_k w[c, k] * in[t - (taps - 1) + k, c]), `in` being the request's inputs: rows of
+// this step, before them the taps - 1 inputs kept in the state, zeros before position 0.
+// state[slot, j, c], j = 0 .. taps - 2, oldest first.  Reads the state only; conv_state_kernel moves it on.
+template <typename T>
+__global__ void causal_conv_kernel(T* __restrict__ out, const T* __restrict__ x, int ld, int column, int channels,
+                                   const float* __restrict__ w, const float* __restrict__ b, int taps,
+                                   const float* __restrict__ state, const int* __restrict__ q_start,
+                                   const int* __restrict__ tok_req, const int* __restrict__ positions,
+                                   const int* __restrict__ state_slot, int silu) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int r = tok_req[t];
+  if (r < 0) return;
+  const int in_step = t - q_start[r];                 // rows of this request before t in this step
+  const int pos = positions[t];
+  const float* st = state + (size_t)state_slot[r] * (taps > 1 ? taps - 1 : 1) * channels;
+  float acc = b ? b[c] : 0.f;
+  for (int k = 0; k < taps; ++k) {
+    const int back = taps - 1 - k;
+    float v = 0.f;
+    if (back <= in_step) v = to_f32(x[(size_t)(t - back) * ld + column + c]);
+    else if (back <= pos) v = st[(size_t)(taps - 1 - (back - in_step)) * channels + c];
+    acc = fmaf(w[(size_t)c * taps + k], v, acc);
+  }
+  out[(size_t)t * channels + c] = from_f32<T>(silu ? silu_f32(acc) : acc);
+}
+
+// The state after the step: the last taps - 1 inputs of each request.  New entry j takes the step's row
+// n - (taps - 1) + j, or, where that lies before the step, the old entry j + n (zero before position 0).
+// Ascending j reads only entries that have not been rewritten yet.
+template <typename T>
+__global__ void conv_state_kernel(float* __restrict__ state, const T* __restrict__ x, int ld, int column, int channels, int taps,
+                                  const int* __restrict__ q_start, const int* __restrict__ positions,
+                                  const int* __restrict__ state_slot) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.x;
+  const int c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= channels) return;
+  const int lo = q_start[r], n = q_start[r + 1] - lo;
+  if (n <= 0) return;
+  const int pos0 = positions[lo];
+  float* st = state + (size_t)state_slot[r] * (taps - 1) * channels;
+  for (int j = 0; j < taps - 1; ++j) {
+    const int row = n - (taps - 1) + j;
+    float v;
+    if (row >= 0) v = to_f32(x[(size_t)(lo + row) * ld + column + c]);
+    else v = pos0 + row >= 0 ? st[(size_t)(j + n) * channels + c] : 0.f;
+    st[(size_t)j * channels + c] = v;
+  }
+}
+
+// ------------------------------------------------------------------ selective scan
+// Per channel c and state n:  S <- exp(dt A[c, n]) S + dt x B_n;  y = sum_n S C_n + D x;  out = y * silu(z),
+// dt = softplus(dt_raw[t, c] + dt_bias[c]).  Eight lanes share a channel, lane l holding states l, l + 8, ...
+// (NPL of them); a block of 128 threads walks 16 channels of one request through its tokens in order.
+template <typename T, int NPL>
+__global__ void __launch_bounds__(128)
+selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float* __restrict__ dt_raw,
+                      const float* __restrict__ dt_bias, const float* __restrict__ A, const T* __restrict__ bc,
+                      const float* __restrict__ D, const T* __restrict__ z, int z_ld, int z_column, int inner, int n_state,
+                      float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ positions,
+                      const int* __restrict__ state_slot) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.y;
+  const int lo = q_start[r], hi = q_start[r + 1];
+  if (hi <= lo) return;
+  const int sub = threadIdx.x & 7;
+  const int c_raw = blockIdx.x * 16 + (threadIdx.x >> 3);
+  const bool live = c_raw < inner;
+  const int c = live ? c_raw : inner - 1;             // lanes past the end shadow the last channel and store nothing
+  float* st = state + ((size_t)state_slot[r] * inner + c) * n_state;
+  const bool from_zero = positions[lo] == 0;
+  float S[NPL], a[NPL];
+#pragma unroll
+  for (int i = 0; i < NPL; ++i) {
+    const int n = sub + 8 * i;
+    S[i] = (n < n_state && !from_zero) ? st[n] : 0.f;
+    a[i] = n < n_state ? A[(size_t)c * n_state + n] : 0.f;
+  }
+  const float bias = dt_bias[c], skip = D[c];
+  for (int t = lo; t < hi; ++t) {
+    const float x = to_f32(xc[(size_t)t * inner + c]);
+    const float dt = softplus_f32(dt_raw[(size_t)t * inner + c] + bias);
+    const T* bcr = bc + (size_t)t * 2 * n_state;
+    const float dx = dt * x;
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = sub + 8 * i;
+      if (n < n_state) {
+        S[i] = fmaf(expf(dt * a[i]), S[i], dx * to_f32(bcr[n]));
+        acc = fmaf(S[i], to_f32(bcr[n_state + n]), acc);
+      }
+    }
+    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+    if (sub == 0 && live) {
+      const float g = to_f32(z[(size_t)t * z_ld + z_column + c]);
+      out[(size_t)t * inner + c] = from_f32<T>((acc + skip * x) * silu_f32(g));
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < NPL; ++i) {
+      const int n = sub + 8 * i;
+      if (n < n_state) st[n] = S[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ gated delta rule
+// Per value head h (query/key head c = h / (heads / kv_heads)) and token, with k, q scaled to unit length
+// (q also by q_scale), beta = sigmoid(b), g = exp(-rate[h] * softplus(a + dt_bias[h])):
+//     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
+// A column S[:, j] is independent of the others: eight lanes share a column, lane l holding rows l, l + 8, ...
+// (RPL of them); a block of 128 threads walks 16 columns of one head of one request through its tokens.
+// qkv rows: [q: kv_heads * d | k: kv_heads * d | v: heads * dv];  ba rows: [b: heads | a: heads] float32.
+template <typename T, int RPL>
+__global__ void __launch_bounds__(128)
+gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, const float* __restrict__ ba,
+                        const float* __restrict__ rate, const float* __restrict__ dt_bias, float* __restrict__ state,
+                        const int* __restrict__ q_start, const int* __restrict__ positions, const int* __restrict__ state_slot,
+                        int heads, int kv_heads, int d, int dv, float unit_eps, float q_scale) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int lo = q_start[r], hi = q_start[r + 1];
+  if (hi <= lo) return;
+  const int sub = threadIdx.x & 7;
+  const int j_raw = blockIdx.x * 16 + (threadIdx.x >> 3);
+  const bool live = j_raw < dv;
+  const int j = live ? j_raw : dv - 1;
+  const int c = h / (heads / kv_heads);
+  const int ld = 2 * kv_heads * d + heads * dv;
+  float* st = state + (((size_t)state_slot[r] * heads + h) * d) * dv + j;
+  const bool from_zero = positions[lo] == 0;
+  float S[RPL];
+#pragma unroll
+  for (int i = 0; i < RPL; ++i) {
+    const int row = sub + 8 * i;
+    S[i] = (row < d && !from_zero) ? st[(size_t)row * dv] : 0.f;
+  }
+  const float rate_h = rate[h], bias_h = dt_bias[h];
+  for (int t = lo; t < hi; ++t) {
+    const T* row = qkv + (size_t)t * ld;
+    float q[RPL], k[RPL];
+    float qq = 0.f, kk = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      const int e = sub + 8 * i;
+      q[i] = e < d ? to_f32(row[c * d + e]) : 0.f;
+      k[i] = e < d ? to_f32(row[(kv_heads + c) * d + e]) : 0.f;
+      qq = fmaf(q[i], q[i], qq);
+      kk = fmaf(k[i], k[i], kk);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) {
+      qq += __shfl_xor_sync(0xffffffffu, qq, o);
+      kk += __shfl_xor_sync(0xffffffffu, kk, o);
+    }
+    const float qn = q_scale / sqrtf(qq + unit_eps), kn = 1.0f / sqrtf(kk + unit_eps);
+    const float v = to_f32(row[2 * kv_heads * d + h * dv + j]);
+    const float beta = 1.0f / (1.0f + expf(-ba[(size_t)t * 2 * heads + h]));
+    const float g = expf(-rate_h * softplus_f32(ba[(size_t)t * 2 * heads + heads + h] + bias_h));
+    float dot = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      k[i] *= kn;
+      q[i] *= qn;
+      S[i] *= g;
+      dot = fmaf(S[i], k[i], dot);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+    const float u = beta * (v - dot);
+    float acc = 0.f;
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      S[i] = fmaf(k[i], u, S[i]);
+      acc = fmaf(S[i], q[i], acc);
+    }
+#pragma unroll
+    for (int o = 1; o < 8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+    if (sub == 0 && live) out[(size_t)t * heads * dv + h * dv + j] = acc;
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      const int row = sub + 8 * i;
+      if (row < d) st[(size_t)row * dv] = S[i];
+    }
+  }
+}
+
+// ------------------------------------------------------------------ per-head norm with an output gate
+// out[t, column + h * dv + e] = o[t, h, e] * rsqrt(mean_e(o^2) + eps) * w[e] * silu(gate[t, gate_column + h * dv + e]) * scale.
+// One warp per (token, head).
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_head_norm_kernel(T* __restrict__ out, int out_ld, int column, const float* __restrict__ o, const float* __restrict__ w,
+                       float eps, const T* __restrict__ gate, int gate_ld, int gate_column, int tokens, int heads, int dv,
+                       float scale) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const size_t item = (size_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (size_t)tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item % heads);
+  const float* src = o + (size_t)t * heads * dv + (size_t)h * dv;
+  float ss = 0.f;
+  for (int e = lane; e < dv; e += 32) ss = fmaf(src[e], src[e], ss);
+  ss = warp_sum(ss);
+  const float rrms = 1.0f / sqrtf(ss / (float)dv + eps);
+  for (int e = lane; e < dv; e += 32) {
+    const float g = to_f32(gate[(size_t)t * gate_ld + gate_column + h * dv + e]);
+    out[(size_t)t * out_ld + column + h * dv + e] = from_f32<T>(src[e] * rrms * w[e] * silu_f32(g) * scale);
+  }
+}
+
+// ------------------------------------------------------------------ launchers
+template <typename T>
+int causal_conv(void* out, const void* x, int ld, int column, int channels, const float* w, const float* b, int taps, float* state,
+                const int* q_start, const int* tok_req, const int* positions, const int* state_slot, int tokens, int requests,
+                int silu, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && requests >= 0 && channels > 0 && taps > 0 && column >= 0 && column + channels <= ld,
+              "causal_conv: bad sizes tokens=%d channels=%d taps=%d column=%d ld=%d", tokens, channels, taps, column, ld);
+  if (tokens == 0) return 0;
+  const dim3 block(128), tiles((channels + 127) / 128);
+  PTL_REQUIRE(tiles.x <= 65535, "causal_conv: too many channels (%d)", channels);
+  if (int rc = launch_kernel("causal_conv", causal_conv_kernel<T>, dim3(tokens, tiles.x), block, 0, as_stream(stream), (T*)out,
+                             (const T*)x, ld, column, channels, w, b, taps, (const float*)state, q_start, tok_req, positions,
+                             state_slot, silu))
+    return rc;
+  if (taps == 1 || requests == 0) return 0;
+  return launch_kernel("conv_state", conv_state_kernel<T>, dim3(requests, tiles.x), block, 0, as_stream(stream), state, (const T*)x,
+                       ld, column, channels, taps, q_start, positions, state_slot);
+}
+
+template <typename T>
+int selective_scan(void* out, const void* xc, const float* dt_raw, const float* dt_bias, const float* A, const void* bc,
+                   const float* D, const void* z, int z_ld, int z_column, int inner, int n_state, float* state, const int* q_start,
+                   const int* positions, const int* state_slot, int requests, void* stream) {
+  PTL_REQUIRE(requests >= 0 && inner > 0 && n_state > 0 && n_state <= 256 && z_column >= 0 && z_column + inner <= z_ld,
+              "selective_scan: bad sizes inner=%d state=%d (at most 256)", inner, n_state);
+  PTL_REQUIRE(requests <= 65535, "selective_scan: at most 65535 requests per step, got %d", requests);
+  if (requests == 0) return 0;
+  const dim3 grid((inner + 15) / 16, requests), block(128);
+#define PTL_SCAN(NPL) return launch_kernel("selective_scan", selective_scan_kernel<T, NPL>, grid, block, 0, as_stream(stream), \
+    (T*)out, (const T*)xc, dt_raw, dt_bias, A, (const T*)bc, D, (const T*)z, z_ld, z_column, inner, n_state, state, q_start, \
+    positions, state_slot)
+  const int per_lane = (n_state + 7) / 8;
+  if (per_lane <= 1) PTL_SCAN(1);
+  if (per_lane <= 2) PTL_SCAN(2);
+  if (per_lane <= 3) PTL_SCAN(3);
+  if (per_lane <= 4) PTL_SCAN(4);
+  if (per_lane <= 8) PTL_SCAN(8);
+  if (per_lane <= 16) PTL_SCAN(16);
+  PTL_SCAN(32);
+#undef PTL_SCAN
+}
+
+template <typename T>
+int gated_delta_rule(float* out, const void* qkv, const float* ba, const float* rate, const float* dt_bias, float* state,
+                     const int* q_start, const int* positions, const int* state_slot, int requests, int heads, int kv_heads, int d,
+                     int dv, float unit_eps, float q_scale, void* stream) {
+  PTL_REQUIRE(requests >= 0 && heads > 0 && kv_heads > 0 && heads % kv_heads == 0 && d > 0 && d <= 256 && dv > 0,
+              "gated_delta_rule: bad sizes heads=%d kv_heads=%d d=%d (at most 256) dv=%d", heads, kv_heads, d, dv);
+  PTL_REQUIRE(requests <= 65535 && heads <= 65535, "gated_delta_rule: at most 65535 requests and heads");
+  if (requests == 0) return 0;
+  const dim3 grid((dv + 15) / 16, heads, requests), block(128);
+#define PTL_DELTA(RPL) return launch_kernel("gated_delta_rule", gated_delta_rule_kernel<T, RPL>, grid, block, 0, as_stream(stream), \
+    out, (const T*)qkv, ba, rate, dt_bias, state, q_start, positions, state_slot, heads, kv_heads, d, dv, unit_eps, q_scale)
+  const int per_lane = (d + 7) / 8;
+  if (per_lane <= 2) PTL_DELTA(2);
+  if (per_lane <= 4) PTL_DELTA(4);
+  if (per_lane <= 8) PTL_DELTA(8);
+  if (per_lane <= 12) PTL_DELTA(12);
+  if (per_lane <= 16) PTL_DELTA(16);
+  PTL_DELTA(32);
+#undef PTL_DELTA
+}
+
+template <typename T>
+int gated_head_norm(void* out, int out_ld, int column, const float* o, const float* w, float eps, const void* gate, int gate_ld,
+                    int gate_column, int tokens, int heads, int dv, float scale, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && heads > 0 && dv > 0 && eps > 0.f && column >= 0 && column + heads * dv <= out_ld &&
+              gate_column >= 0 && gate_column + heads * dv <= gate_ld, "gated_head_norm: bad sizes tokens=%d heads=%d dv=%d",
+              tokens, heads, dv);
+  if (tokens == 0) return 0;
+  const size_t items = (size_t)tokens * heads;
+  return launch_kernel("gated_head_norm", gated_head_norm_kernel<T>, dim3((unsigned)((items + 7) / 8)), dim3(256), 0,
+                       as_stream(stream), (T*)out, out_ld, column, o, w, eps, (const T*)gate, gate_ld, gate_column, tokens, heads,
+                       dv, scale);
+}
+
+}  // namespace ptl
+
+#define PTL_RECURRENT(SUFFIX, TYPE)                                                                                               \
+  PTL_EXPORT int ptl_causal_conv##SUFFIX(void* out, const void* x, int ld, int column, int channels, const float* w,               \
+                                         const float* b, int taps, float* state, const int* q_start, const int* tok_req,           \
+                                         const int* positions, const int* state_slot, int tokens, int requests, int silu,         \
+                                         void* stream) {                                                                          \
+    return ptl::causal_conv<TYPE>(out, x, ld, column, channels, w, b, taps, state, q_start, tok_req, positions, state_slot, tokens, \
+                                  requests, silu, stream);                                                                        \
+  }                                                                                                                               \
+  PTL_EXPORT int ptl_selective_scan##SUFFIX(void* out, const void* xc, const float* dt_raw, const float* dt_bias, const float* A,  \
+                                            const void* bc, const float* D, const void* z, int z_ld, int z_column, int inner,      \
+                                            int n_state, float* state, const int* q_start, const int* positions,                  \
+                                            const int* state_slot, int requests, void* stream) {                                  \
+    return ptl::selective_scan<TYPE>(out, xc, dt_raw, dt_bias, A, bc, D, z, z_ld, z_column, inner, n_state, state, q_start,        \
+                                     positions, state_slot, requests, stream);                                                    \
+  }                                                                                                                               \
+  PTL_EXPORT int ptl_gated_delta_rule##SUFFIX(float* out, const void* qkv, const float* ba, const float* rate,                     \
+                                              const float* dt_bias, float* state, const int* q_start, const int* positions,       \
+                                              const int* state_slot, int requests, int heads, int kv_heads, int d, int dv,        \
+                                              float unit_eps, float q_scale, void* stream) {                                      \
+    return ptl::gated_delta_rule<TYPE>(out, qkv, ba, rate, dt_bias, state, q_start, positions, state_slot, requests, heads,        \
+                                       kv_heads, d, dv, unit_eps, q_scale, stream);                                               \
+  }                                                                                                                               \
+  PTL_EXPORT int ptl_gated_head_norm##SUFFIX(void* out, int out_ld, int column, const float* o, const float* w, float eps,         \
+                                             const void* gate, int gate_ld, int gate_column, int tokens, int heads, int dv,        \
+                                             float scale, void* stream) {                                                         \
+    return ptl::gated_head_norm<TYPE>(out, out_ld, column, o, w, eps, gate, gate_ld, gate_column, tokens, heads, dv, scale,        \
+                                      stream);                                                                                    \
+  }
+PTL_RECURRENT(_f32, float)
+PTL_RECURRENT(_bf16, __nv_bfloat16)

@@ -28,9 +28,18 @@ class GroupStepView:
 class LayerCacheView:
     """The cache entry one run of a layer uses."""
     group: Optional[GroupStepView]
-    kv: Optional[torch.Tensor]      # [pages, 2, kv_heads, page_size, head_dim] of this entry
+    kv: Optional[torch.Tensor]      # [pages, 2, kv_heads, page_size, head_dim] of this entry; with values of another
+                                    # size [pages, kv_heads * page_size * (head_dim + value_dim)], keys first
     state: Optional[torch.Tensor]   # [slots, *state_shape] per-request state of this entry
     write: bool = True              # False: read what another run of a layer stored
+    states: Dict[str, torch.Tensor] = field(default_factory=dict)   # named per-request states: [slots, *shape] float32
+
+    def member(self, prefix: str) -> "LayerCacheView":
+        """The view of one member of a mixer made of several: the states whose names start with
+        ``prefix`` + ".", under their own names."""
+        cut = len(prefix) + 1
+        return LayerCacheView(self.group, self.kv, self.state, self.write,
+                              {k[cut:]: v for k, v in self.states.items() if k.startswith(prefix + ".")})
 
 
 @dataclass
@@ -49,5 +58,6 @@ class StepContext:
     max_q_len: int = 0
     max_ctx_len: int = 0
     attn_splits: int = 1
+    tokens: Optional[torch.Tensor] = None   # int32 [T] the step's token ids (set by the model's forward pass)
     # integer lists the operator set asked for (``ops.plan_step``): name -> ``StepWork``
     work: Dict[str, Any] = field(default_factory=dict)

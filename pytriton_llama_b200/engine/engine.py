@@ -201,9 +201,9 @@ class Engine:
         esize = torch.empty((), dtype=self.config.dtype).element_size()
         per_page: Dict[tuple, int] = {}
         for need in entries.values():
-            if need.kind in ("full", "window"):
+            if need.kind in ("full", "window", "chunk"):
                 k = need.group_key()
-                per_page[k] = per_page.get(k, 0) + 2 * need.kv_heads * need.head_dim * self.config.page_size * esize
+                per_page[k] = per_page.get(k, 0) + need.kv_heads * (need.head_dim + need.v_dim) * self.config.page_size * esize
         if not per_page:
             return 1
         bytes_per_page = sum(per_page.values())   # one page in every group
@@ -412,7 +412,8 @@ class Engine:
         def cache_view(entry: int, write: bool) -> LayerCacheView:
             g = cache.entry_group[entry]
             grp = cache.groups[g]
-            return LayerCacheView(group=groups.get(g), kv=grp.kv.get(entry), state=grp.state.get(entry), write=write)
+            return LayerCacheView(group=groups.get(g), kv=grp.kv.get(entry), state=grp.state.get(entry), write=write,
+                                  states=grp.states.get(entry, {}))
         return ctx, cache_view
 
     def _choose_splits(self, tokens: int, max_ctx: int) -> int:
@@ -429,7 +430,7 @@ class Engine:
         holds prompt portions.  Only for models whose mixers keep nothing but paged keys and values."""
         if not self.config.compiled_model or self.device.type != "cuda" or self.config.timing:
             return 0          # (timing brackets every operator with events, which a capture cannot hold)
-        if any(not grp.paged or grp.state for grp in self.cache.groups):
+        if any(not grp.paged or grp.state or grp.states for grp in self.cache.groups):
             return 0
         if batch.max_q_len != 1:
             return self._shape_bucket(batch) if self.config.capture_mixed_steps else 0

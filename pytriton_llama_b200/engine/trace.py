@@ -21,7 +21,7 @@ import sys
 from pathlib import Path
 
 PAGE_SIZE = 16
-LIVE_REQUESTS = 8
+LIVE_REQUESTS = 4
 
 
 def main(argv=None) -> int:

@@ -39,6 +39,8 @@ class DecoderModel:
         }
         if self.spec.lm_head is not None:
             out[self.spec.lm_head] = TensorSpec((self.spec.vocab_size, self.spec.hidden_size))
+        for shared in self.spec.shared_tensors.values():
+            out[shared.name] = shared.spec
         roots = [(b, s) for b, s in zip(self.blocks, self.spec.layers)] + [(self.final_norm, self.spec.final_norm)]
         for root, rspec in roots:
             for part, pspec in _walk(root, rspec):
@@ -54,12 +56,18 @@ class DecoderModel:
             self.lm_head = self.embedding
         else:
             self.lm_head = tensors[self.spec.lm_head].to(device=rt.device, dtype=rt.dtype).contiguous()
+        for key, shared in self.spec.shared_tensors.items():
+            rt.shared[key] = tensors[shared.name].to(device=rt.device, dtype=rt.dtype).contiguous()
         roots = [(b, s) for b, s in zip(self.blocks, self.spec.layers)] + [(self.final_norm, self.spec.final_norm)]
         for root, rspec in roots:
             for part, pspec in _walk(root, rspec):
                 specs = part.tensor_specs()
                 if specs:
                     part.load({local: tensors.get(pspec.tensors[local]) for local in specs})
+        for root, rspec in roots:                      # members first: a part made of others joins what they loaded
+            for part, _ in reversed(list(_walk(root, rspec))):
+                if hasattr(part, "after_load"):
+                    part.after_load()
 
     # ------------------------------------------------------------------ cache
     def cache_entries(self) -> Dict[int, CacheNeed]:
@@ -80,8 +88,15 @@ class DecoderModel:
         begin = getattr(ops, "begin_forward", None)
         if begin is not None:
             begin()             # (what an operator set keeps per step, such as rotary angles, starts afresh)
-        x = ops.embed(token_ids, self.embedding)
-        residual = None
+        ctx.tokens = token_ids
+        if self.spec.position_vector is not None or self.spec.embedding_scale != 1.0:
+            # scaled rows plus the position vector, in float32: this is the stream itself, nothing is left to add
+            if self.spec.position_vector not in (None, "sinusoidal"):
+                raise ValueError(f"unknown position vector {self.spec.position_vector!r}")
+            x, residual = None, ops.embed_scaled(token_ids, self.embedding, self.spec.embedding_scale, ctx.positions,
+                                                 self.spec.position_base if self.spec.position_vector else 0.0)
+        else:
+            x, residual = ops.embed(token_ids, self.embedding), None
         run = self.spec.run_order
         for i, e in enumerate(run):
             block = self.blocks[e.layer]
@@ -93,4 +108,7 @@ class DecoderModel:
         if logit_rows is None or logit_rows.numel() == 0:
             return None
         y, _ = self.final_norm.forward(x, residual, rows=logit_rows)
-        return ops.linear(y, self.lm_head, out_dtype=torch.float32)
+        logits = ops.linear(y, self.lm_head, out_dtype=torch.float32)
+        if self.spec.logit_softcap > 0:
+            ops.softcap(logits, self.spec.logit_softcap)
+        return logits

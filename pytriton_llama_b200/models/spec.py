@@ -7,7 +7,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional
 
-from ..parts.base import PartSpec
+from ..parts.base import PartSpec, TensorSpec
 
 
 @dataclass
@@ -18,6 +18,13 @@ class RunEntry:
     layer: int
     cache: int
     write: bool = True
+
+
+@dataclass(frozen=True)
+class SharedTensor:
+    """A tensor of the checkpoint that belongs to no single layer."""
+    name: str                           # checkpoint name
+    spec: TensorSpec
 
 
 @dataclass
@@ -33,6 +40,11 @@ class ModelSpec:
     initializer_range: float = 0.02
     eos_token_ids: List[int] = field(default_factory=list)
     max_position_embeddings: Optional[int] = None
+    embedding_scale: float = 1.0        # the looked-up row is multiplied by this
+    position_vector: Optional[str] = None   # "sinusoidal": entry 2i, 2i+1 of the stream get sin, cos(p * base^(-2i/width)) added
+    position_base: float = 10000.0
+    logit_softcap: float = 0.0          # > 0: logits <- cap * tanh(logits / cap)
+    shared_tensors: Dict[str, "SharedTensor"] = field(default_factory=dict)   # read by parts of every layer (Runtime.shared)
 
     def validate(self) -> None:
         n = len(self.layers)

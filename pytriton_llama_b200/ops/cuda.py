@@ -28,6 +28,20 @@ _SIGNATURES = {
     "ptl_add_rmsnorm": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr],
     "ptl_silu_mul": [_ptr, _ptr, _c_int, _c_int, _ptr],
     "ptl_rope_kv_write": [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _ptr],
+    "ptl_add_bias_rmsnorm": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr],
+    "ptl_embed_scaled": [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_f, _ptr, _ptr],
+    "ptl_clamped_glu": [_ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _c_f, _c_f, _ptr],
+    "ptl_token_side": [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr],
+    "ptl_causal_conv": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int,
+                        _c_int, _ptr],
+    "ptl_selective_scan": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr,
+                           _c_int, _ptr],
+    "ptl_gated_delta_rule": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f,
+                             _c_f, _ptr],
+    "ptl_gated_head_norm": [_ptr, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr],
+    "ptl_kv_write_normed": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_f, _ptr],
+    "ptl_chunk_attention": [_ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int,
+                            _c_int, _c_int, _c_int, _c_f, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr],
     "ptl_paged_attention_simt": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int,
                                  _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr],
 }
@@ -121,6 +135,8 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_sample.restype = _c_int
     lib.ptl_sample_work_words.argtypes = []
     lib.ptl_sample_work_words.restype = _c_int
+    lib.ptl_softcap.argtypes = [_ptr, _c_ll, _c_f, _ptr]
+    lib.ptl_softcap.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
     lib.ptl_set_dependent_launch.argtypes = [_c_int]
     lib.ptl_get_dependent_launch.restype = _c_int
@@ -213,6 +229,9 @@ class CudaOps:
     # ------------------------------------------------------------------ timing by class of kernels (diagnostic)
     KERNEL_CLASSES = {
         "embed": "elementwise", "take_tokens": "elementwise", "silu_mul": "elementwise", "add_rmsnorm": "norm",
+        "embed_scaled": "elementwise", "softcap": "elementwise", "clamped_glu": "elementwise", "token_side": "token_input",
+        "causal_conv": "recurrent", "selective_scan": "recurrent", "gated_delta_rule": "recurrent", "gated_head_norm": "norm",
+        "kv_write_normed": "attention", "chunk_attention": "attention",
         "linear": "product", "linear_add": "product", "gate_up_silu": "product", "gemm_tc": "product",
         "_qkv_rope_product": "product", "rope_kv_write": "rope", "_rope_table": "rope",
         "paged_attention": "attention", "_attention_tensor_cores": "attention",
@@ -309,8 +328,10 @@ class CudaOps:
 
     def add_rmsnorm(self, x: Optional[torch.Tensor], residual: Optional[torch.Tensor], weight: torch.Tensor,
                     eps: float, rows: Optional[torch.Tensor] = None,
-                    dtype: Optional[torch.dtype] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
-        """y = rmsnorm(residual + x) * weight, the sum kept as the new float32 residual.
+                    dtype: Optional[torch.dtype] = None,
+                    bias: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
+        """y = rmsnorm(residual + x) * weight, the sum kept as the new float32 residual.  ``bias``
+        (float32 [hidden]) is added into the sum as well.
 
         Without ``rows`` the residual tensor is updated in place (created from ``x`` when None).
         With ``rows`` (int32 indices) only those rows are normed and no residual is written."""
@@ -332,6 +353,12 @@ class CudaOps:
             n_out = src.shape[0]
             res_out = residual if residual is not None else self.empty((n_out, hidden), torch.float32)
         y = self.empty((n_out, hidden), dtype)
+        if bias is not None:
+            self._want(bias, "bias", torch.float32)
+            fn = getattr(self.lib, "ptl_add_bias_rmsnorm" + _suffix(dtype))
+            self._check(fn(_p(y), _p(res_out), _p(residual), _p(x), _p(bias), _p(weight), _p(rows), n_out, hidden,
+                           float(eps), self._stream()))
+            return y, res_out
         fn = getattr(self.lib, "ptl_add_rmsnorm" + _suffix(dtype))
         self._check(fn(_p(y), _p(res_out), _p(residual), _p(x), _p(weight), _p(rows), n_out, hidden,
                        float(eps), self._stream()))
@@ -784,6 +811,163 @@ class CudaOps:
             self._check(self.lib.ptl_prefill_attention_bf16(
                 _p(out), _p(q), _p(cache), _p(block_table), _p(tiles.tensor), n_tiles, q.shape[1],
                 nq * d, block_table.shape[1], nq, nkv, d, page_size, float(scale), int(window), num_pages, stream))
+
+    # ------------------------------------------------------------------ the float32 stream, recurrent and chunked mixers
+    def embed_scaled(self, ids: torch.Tensor, table: torch.Tensor, scale: float, positions: torch.Tensor,
+                     base: float) -> torch.Tensor:
+        """float32 [T, width]: table[ids] * scale, plus (``base`` > 0) the sinusoidal position vector whose entries
+        2i and 2i + 1 are sin and cos of position * base^(-2i / width)."""
+        self._want(ids, "ids", torch.int32)
+        self._want(positions, "positions", torch.int32)
+        self._want(table, "table")
+        width = table.shape[1]
+        freq = None
+        if base:
+            memo = getattr(self, "_position_freq", None)
+            if memo is None or memo[0] != (width, float(base)):
+                i = torch.arange((width + 1) // 2, dtype=torch.float64)
+                memo = self._position_freq = ((width, float(base)), (float(base) ** (-2.0 * i / width)).to(self.device))
+            freq = memo[1]
+        out = self.empty((ids.shape[0], width), torch.float32)
+        fn = getattr(self.lib, "ptl_embed_scaled" + _suffix(table.dtype))
+        self._check(fn(_p(out), _p(table), _p(ids), _p(positions), _p(freq), ids.shape[0], width, table.shape[0], float(scale),
+                       _p(self._status), self._stream()))
+        return out
+
+    def softcap(self, logits: torch.Tensor, cap: float) -> None:
+        """logits <- cap * tanh(logits / cap), in place."""
+        self._want(logits, "logits", torch.float32)
+        self._check(self.lib.ptl_softcap(_p(logits), logits.numel(), float(cap), self._stream()))
+
+    def clamped_glu(self, gu: torch.Tensor, bias: Optional[torch.Tensor], limit: float, alpha: float, up_shift: float) -> torch.Tensor:
+        """gu [T, 2*inter] (gate columns first) + bias -> min(g, limit) * sigmoid(alpha * g) * (clamp(u, +-limit) + up_shift)."""
+        self._want(gu, "gate_up")
+        if bias is not None:
+            self._want(bias, "bias", torch.float32)
+        tokens, two_i = gu.shape
+        out = self.empty((tokens, two_i // 2), gu.dtype)
+        fn = getattr(self.lib, "ptl_clamped_glu" + _suffix(gu.dtype))
+        self._check(fn(_p(out), _p(gu), _p(bias), tokens, two_i // 2, float(limit), float(alpha), float(up_shift), self._stream()))
+        return out
+
+    def token_side(self, residual: torch.Tensor, x: Optional[torch.Tensor], bias: Optional[torch.Tensor], tokens: torch.Tensor,
+                   table: torch.Tensor, column: int, dim: int, w_gate: torch.Tensor, w_proj: torch.Tensor, norm_w: torch.Tensor,
+                   eps: float) -> None:
+        """residual (float32, in place) <- s + rmsnorm(W_proj (gelu_tanh(W_gate s) * table[token, column:column+dim])) * norm_w
+        with s = residual + x + bias."""
+        self._want(residual, "residual", torch.float32)
+        self._want(tokens, "tokens", torch.int32)
+        self._want(table, "table")
+        self._want(w_gate, "w_gate", table.dtype)
+        self._want(w_proj, "w_proj", table.dtype)
+        self._want(norm_w, "norm weight", torch.float32)
+        if x is not None:
+            self._want(x, "x", table.dtype)
+        if bias is not None:
+            self._want(bias, "bias", torch.float32)
+        fn = getattr(self.lib, "ptl_token_side" + _suffix(table.dtype))
+        self._check(fn(_p(residual), _p(x), _p(bias), _p(tokens), _p(table), table.shape[1], int(column), int(dim), table.shape[0],
+                       _p(w_gate), _p(w_proj), _p(norm_w), residual.shape[0], residual.shape[1], float(eps), self._stream()))
+
+    def causal_conv(self, x: torch.Tensor, column: int, channels: int, w: torch.Tensor, b: Optional[torch.Tensor],
+                    state: torch.Tensor, ctx, silu: bool = True) -> torch.Tensor:
+        """Causal convolution per channel over columns ``column``.. of x [T, ld] with the taps w [channels, taps] (the last
+        is the current token's); ``state`` [slots, taps - 1, channels] holds each request's last inputs and is moved on."""
+        self._want(x, "x")
+        self._want(w, "conv weight", torch.float32)
+        self._want(state, "conv state", torch.float32)
+        if b is not None:
+            self._want(b, "conv bias", torch.float32)
+        taps = w.shape[1]
+        if w.shape[0] != channels or state.shape[1] != max(taps - 1, 1) or state.shape[2] != channels:
+            raise KernelError(f"causal_conv: weight {list(w.shape)} and state {list(state.shape)} do not fit {channels} channels")
+        out = self.empty((x.shape[0], channels), x.dtype)
+        fn = getattr(self.lib, "ptl_causal_conv" + _suffix(x.dtype))
+        self._check(fn(_p(out), _p(x), x.shape[1], int(column), int(channels), _p(w), _p(b), taps, _p(state), _p(ctx.q_start),
+                       _p(ctx.tok_req), _p(ctx.positions), _p(ctx.state_slot), x.shape[0], ctx.num_requests, int(bool(silu)),
+                       self._stream()), kernels=2 if taps > 1 else 1)
+        return out
+
+    def selective_scan(self, xc: torch.Tensor, dt: torch.Tensor, dt_b: torch.Tensor, A: torch.Tensor, bc: torch.Tensor,
+                       D: torch.Tensor, xz: torch.Tensor, z_column: int, state: torch.Tensor, ctx) -> torch.Tensor:
+        """The scan of ``parts/scan.py``: xc [T, inner], dt float32 [T, inner] before bias and softplus, A float32
+        [inner, n], bc [T, 2n] (B | C), the gate z in columns ``z_column``.. of xz; state float32 [slots, inner, n]."""
+        inner, n = A.shape
+        self._want(xc, "xc")
+        self._want(bc, "bc", xc.dtype)
+        self._want(xz, "xz", xc.dtype)
+        for name, t in (("dt", dt), ("dt bias", dt_b), ("A", A), ("D", D), ("scan state", state)):
+            self._want(t, name, torch.float32)
+        if xc.shape[1] != inner or dt.shape != xc.shape or bc.shape[1] != 2 * n or tuple(state.shape[1:]) != (inner, n):
+            raise KernelError("selective_scan: shapes do not fit")
+        out = self.empty(xc.shape, xc.dtype)
+        fn = getattr(self.lib, "ptl_selective_scan" + _suffix(xc.dtype))
+        self._check(fn(_p(out), _p(xc), _p(dt), _p(dt_b), _p(A), _p(bc), _p(D), _p(xz), xz.shape[1], int(z_column), inner, n,
+                       _p(state), _p(ctx.q_start), _p(ctx.positions), _p(ctx.state_slot), ctx.num_requests, self._stream()))
+        return out
+
+    def gated_delta_rule(self, qkv: torch.Tensor, ba: torch.Tensor, rate: torch.Tensor, dt_bias: torch.Tensor, state: torch.Tensor,
+                         ctx, H: int, G: int, d: int, dv: int, unit_eps: float, q_scale: float) -> torch.Tensor:
+        """The recurrence of ``parts/delta_rule.py``: qkv [T, q | k | v] after convolution, ba float32 [T, 2H]; returns the
+        heads' read-outs, float32 [T, H*dv]; state float32 [slots, H, d, dv]."""
+        self._want(qkv, "qkv")
+        for name, t in (("ba", ba), ("rate", rate), ("dt_bias", dt_bias), ("state", state)):
+            self._want(t, name, torch.float32)
+        if qkv.shape[1] != 2 * G * d + H * dv or ba.shape[1] != 2 * H or tuple(state.shape[1:]) != (H, d, dv):
+            raise KernelError("gated_delta_rule: shapes do not fit")
+        out = self.empty((qkv.shape[0], H * dv), torch.float32)
+        fn = getattr(self.lib, "ptl_gated_delta_rule" + _suffix(qkv.dtype))
+        self._check(fn(_p(out), _p(qkv), _p(ba), _p(rate), _p(dt_bias), _p(state), _p(ctx.q_start), _p(ctx.positions),
+                       _p(ctx.state_slot), ctx.num_requests, H, G, d, dv, float(unit_eps), float(q_scale), self._stream()))
+        return out
+
+    def gated_head_norm(self, o: torch.Tensor, weight: torch.Tensor, eps: float, gate: torch.Tensor, gate_column: int, H: int,
+                        dv: int, out: torch.Tensor, column: int, scale: float) -> None:
+        """out[:, column + h*dv + e] = o[:, h, e] / rms_e(o[:, h]) * weight[e] * silu(gate[:, gate_column + h*dv + e]) * scale."""
+        self._want(o, "o", torch.float32)
+        self._want(weight, "norm weight", torch.float32)
+        self._want(gate, "gate")
+        self._want(out, "out", gate.dtype)
+        fn = getattr(self.lib, "ptl_gated_head_norm" + _suffix(gate.dtype))
+        self._check(fn(_p(out), out.shape[1], int(column), _p(o), _p(weight), float(eps), _p(gate), gate.shape[1], int(gate_column),
+                       o.shape[0], H, dv, float(scale), self._stream()))
+
+    def kv_write_normed(self, qkv: torch.Tensor, bias: Optional[torch.Tensor], slots: torch.Tensor, cache: torch.Tensor, H: int,
+                        G: int, d: int, dv: int, page_size: int, eps: float) -> None:
+        """Stores k (+ bias) and v (+ bias, divided by its root mean square per head when eps > 0) of qkv [T, q | k | v]
+        in the tokens' slots of a cache whose pages hold keys, then values."""
+        self._want(qkv, "qkv")
+        self._want(cache, "cache", qkv.dtype)
+        self._want(slots, "slots", torch.int32)
+        if bias is not None:
+            self._want(bias, "bias", torch.float32)
+        if qkv.shape[1] != H * d + G * (d + dv) or cache[0].numel() != G * page_size * (d + dv):
+            raise KernelError("kv_write_normed: shapes do not fit")
+        fn = getattr(self.lib, "ptl_kv_write_normed" + _suffix(qkv.dtype))
+        self._check(fn(_p(cache), _p(qkv), _p(bias), _p(slots), qkv.shape[0], H, G, d, dv, page_size, cache.shape[0] * page_size,
+                       float(eps), self._stream()))
+
+    def chunk_attention(self, qkv: torch.Tensor, bias: Optional[torch.Tensor], cache: torch.Tensor, block_table: torch.Tensor,
+                        tok_req: torch.Tensor, positions: torch.Tensor, H: int, G: int, d: int, dv: int, page_size: int,
+                        scale: float, chunk: int, r1: Optional[torch.Tensor], r2: Optional[torch.Tensor],
+                        talk: Optional[torch.Tensor], out: torch.Tensor, column: int, out_scale: float, max_keys: int = 0) -> None:
+        """The attention of ``parts/chunk_attention.py`` for every token of the step; the heads' outputs times
+        ``out_scale`` go to columns ``column``.. of ``out``.  ``max_keys``: the most keys a query sees (default: the
+        chunk, or every position the block table can name)."""
+        self._want(qkv, "qkv")
+        self._want(cache, "cache", qkv.dtype)
+        self._want(out, "out", qkv.dtype)
+        for name, t in (("block_table", block_table), ("tok_req", tok_req), ("positions", positions)):
+            self._want(t, name, torch.int32)
+        for name, t in (("bias", bias), ("r1", r1), ("r2", r2), ("talk", talk)):
+            if t is not None:
+                self._want(t, name, torch.float32)
+        reach = block_table.shape[1] * page_size
+        max_keys = int(max_keys) or (min(chunk, reach) if chunk else reach)
+        fn = getattr(self.lib, "ptl_chunk_attention" + _suffix(qkv.dtype))
+        self._check(fn(_p(out), out.shape[1], int(column), _p(qkv), qkv.shape[1], _p(bias), _p(cache), _p(block_table),
+                       block_table.shape[1], _p(tok_req), _p(positions), qkv.shape[0], H, G, d, dv, page_size, float(scale),
+                       int(chunk), _p(r1), _p(r2), _p(talk), max_keys, cache.shape[0], float(out_scale), self._stream()))
 
     def token_logprobs(self, logits: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
         """log softmax(logits[row])[tokens[row]] as float32 [rows]."""

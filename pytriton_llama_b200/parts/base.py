@@ -1,7 +1,9 @@
 """Interfaces and registry of the parts a decoder layer is put together from.
 
-A part is one of five categories: ``mixer`` (attention here), ``ffn``, ``norm``, ``position``
-and ``block`` (how the other four are arranged around the residual stream).  A part is described
+A part is one of six categories: ``mixer`` (attention, a selective scan, a delta rule, or several
+side by side), ``ffn``, ``norm``, ``position``, ``token_input`` (a term that depends on the
+token itself, added to the stream inside a layer) and ``block`` (how the others are arranged
+around the residual stream).  A part is described
 by a ``PartSpec`` (kind + its sizes and constants + where its tensors are in the checkpoint) and
 built by ``build_part``; it never sees the model's configuration and does not know which model
 it is in.  New kinds are added with ``register_part`` from anywhere, tests included.
@@ -23,6 +25,10 @@ Contracts (``T`` = tokens of the step, all tensors on the runtime's device):
   step's ``StepContext`` and ``cache`` the ``LayerCacheView`` of the cache entry this run of the
   layer uses (``cache.write`` tells whether this run stores its keys and values);
 * ffn: ``forward(x) -> [T, H]``;
+* a mixer or ffn may leave the bias of its last projection un-added and name it in
+  ``output_bias`` (float32 [H] or None): whoever adds the output into the stream adds it too;
+* token_input: ``apply(residual, x, bias, ctx)`` adds ``x`` (+ ``bias``), then its own term, into
+  the float32 ``residual`` in place;
 * a mixer or ffn with the class attribute ``fuses_residual = True`` is called with
   ``residual=<float32 [T, H]>`` as well and may add its output into it and return None;
 * block: ``forward(x, residual, ctx, cache) -> (x, residual)``.
@@ -34,14 +40,16 @@ from typing import Any, Callable, Dict, Optional, Tuple
 
 import torch
 
-CATEGORIES = ("mixer", "ffn", "norm", "position", "block")
+CATEGORIES = ("mixer", "ffn", "norm", "position", "token_input", "block")
 
 
 @dataclass(frozen=True)
 class TensorSpec:
     shape: Tuple[int, ...]
-    init: str = "normal"      # "normal": N(0, std) | "ones" | "ones_jitter": 1 + N(0, 0.01)
+    init: str = "normal"      # "normal": N(0, std) | "ones" | "ones_jitter": 1 + N(0, 0.01) | "zeros" | "uniform": U(lo, hi)
     optional: bool = False    # may be absent from the checkpoint (the part then gets None)
+    lo: float = 0.0           # bounds of "uniform"
+    hi: float = 1.0
 
 
 @dataclass
@@ -56,17 +64,28 @@ class PartSpec:
 class CacheNeed:
     """What one run of a mixer keeps between steps.
 
-    ``kind``: "full" (every key and value), "window" (only the last ``window`` positions) or
-    "none".  ``state_shape``/``state_dtype``: per-request state of fixed size (None if none)."""
+    ``kind``: "full" (every key and value), "window" (only the last ``window`` positions), "chunk"
+    (only the keys of the block of ``window`` positions, counted from position 0, that the next
+    query lies in) or "none".  ``value_dim``: size of a value head where it differs from
+    ``head_dim`` (0: the same).  ``state_shape``/``state_dtype``: per-request state of fixed size
+    (None if none).  ``states``: further per-request states by name, float32, as (name, shape)
+    pairs; a mixer made of several lists those of all its members."""
     kind: str = "none"
     kv_heads: int = 0
     head_dim: int = 0
     window: int = 0
     state_shape: Optional[Tuple[int, ...]] = None
     state_dtype: Optional[torch.dtype] = None
+    value_dim: int = 0
+    states: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
+
+    @property
+    def v_dim(self) -> int:
+        return self.value_dim or self.head_dim
 
     def group_key(self):
-        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype,
+                self.value_dim, self.states)
 
 
 @dataclass
@@ -75,6 +94,7 @@ class Runtime:
     device: torch.device
     dtype: torch.dtype
     ops: Any
+    shared: Dict[str, torch.Tensor] = field(default_factory=dict)   # tensors of the model that parts of every layer read
 
 
 _REGISTRY: Dict[str, Dict[str, Callable[..., Any]]] = {c: {} for c in CATEGORIES}

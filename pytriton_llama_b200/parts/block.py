@@ -12,19 +12,27 @@ from .base import Part, PartSpec, Runtime, build_part, register_part
 
 @register_part("block", "pre_norm")
 class PreNormBlock(Part):
-    """Nested parts: ``norm1``, ``mixer``, ``norm2``, ``ffn``."""
+    """Nested parts: ``norm1``, ``mixer``; ``norm2`` and ``ffn`` (both or neither: a layer without a
+    feed-forward); optionally ``token_input``, which comes last."""
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
         super().__init__(spec, runtime)
         self.norm1 = build_part("norm", spec.parts["norm1"], runtime)
         self.mixer = build_part("mixer", spec.parts["mixer"], runtime)
-        self.norm2 = build_part("norm", spec.parts["norm2"], runtime)
-        self.ffn = build_part("ffn", spec.parts["ffn"], runtime)
+        if ("norm2" in spec.parts) != ("ffn" in spec.parts):
+            raise ValueError("a block has both norm2 and ffn, or neither")
+        self.norm2 = build_part("norm", spec.parts["norm2"], runtime) if "norm2" in spec.parts else None
+        self.ffn = build_part("ffn", spec.parts["ffn"], runtime) if "ffn" in spec.parts else None
+        self.token_input = build_part("token_input", spec.parts["token_input"], runtime) if "token_input" in spec.parts else None
+        last = self.ffn if self.ffn is not None else self.mixer
+        if self.token_input is None and getattr(last, "output_bias_spec", False):
+            raise ValueError("a block whose last projection leaves its bias out needs a token_input that adds it")
 
     takes_next_norm = True   # forward() accepts the norm part that follows the block
 
     def children(self):
-        return {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "ffn": self.ffn}
+        parts = {"norm1": self.norm1, "mixer": self.mixer, "norm2": self.norm2, "ffn": self.ffn, "token_input": self.token_input}
+        return {k: v for k, v in parts.items() if v is not None}
 
     def cache_need(self):
         return self.mixer.cache_need()
@@ -37,8 +45,15 @@ class PreNormBlock(Part):
         prepared input; a sub-layer reads such an input only if it sets ``accepts_normed``."""
         y, residual = self.norm1.forward(x, residual)
         a = self._run(self.mixer, y, residual, self.norm2, ctx, cache)
-        y, residual = self.norm2.forward(a, residual)
-        return self._run(self.ffn, y, residual, next_norm), residual
+        bias = getattr(self.mixer, "output_bias", None)
+        if self.ffn is not None:
+            y, residual = self.norm2.forward(a, residual, bias=bias) if bias is not None else self.norm2.forward(a, residual)
+            a = self._run(self.ffn, y, residual, None if self.token_input is not None else next_norm)
+            bias = getattr(self.ffn, "output_bias", None)
+        if self.token_input is None:
+            return a, residual
+        self.token_input.apply(residual, a, bias, ctx)      # adds a (+ bias) and its own term into the stream
+        return None, residual
 
     @staticmethod
     def _run(part, y, residual, following_norm, *args):

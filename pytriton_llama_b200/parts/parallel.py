@@ -1,0 +1,61 @@
+"""Several mixers side by side on the same input, added with fixed scales:
+y = sum_m scale_m * mixer_m(h).
+
+Each member writes the input of its output projection, already multiplied by its scale, into its
+columns of one buffer, and one product with the members' output weights side by side gives the sum
+(the members' output biases, scaled, are added by the caller: ``output_bias``).  At most one member
+may keep keys and values in pages; the per-request states of all members are kept under
+"<member>.<name>".
+"""
+from __future__ import annotations
+
+import torch
+
+from .base import CacheNeed, Part, PartSpec, Runtime, build_part, register_part
+
+
+@register_part("mixer", "parallel")
+class ParallelMixers(Part):
+    """params: ``hidden``, ``scales`` {member: factor}.  Nested parts: the members, by name; each has
+    ``inner_width``, ``write_inner``, ``w_o`` and ``output_bias``."""
+
+    def __init__(self, spec: PartSpec, runtime: Runtime):
+        super().__init__(spec, runtime)
+        self.members = {name: build_part("mixer", s, runtime) for name, s in spec.parts.items()}
+        self.scales = {name: float(spec.params["scales"][name]) for name in self.members}
+        self.columns, at = {}, 0
+        for name, m in self.members.items():
+            self.columns[name] = at
+            at += m.inner_width
+        self.inner_width = at
+        self.output_bias_spec = any(getattr(m, "output_bias_spec", False) for m in self.members.values())
+        self.w_o = self.output_bias = None
+
+    def children(self):
+        return dict(self.members)
+
+    def after_load(self) -> None:
+        self.w_o = torch.cat([m.w_o for m in self.members.values()], dim=1).contiguous()
+        for m in self.members.values():
+            m.w_o = None            # the joint weight is the one that is used
+        biases = [m.output_bias * self.scales[name] for name, m in self.members.items() if m.output_bias is not None]
+        self.output_bias = sum(biases[1:], biases[0]).contiguous() if biases else None
+
+    def cache_need(self) -> CacheNeed:
+        needs = {name: m.cache_need() for name, m in self.members.items()}
+        paged = [n for n in needs.values() if n.kind != "none"]
+        if len(paged) > 1:
+            raise ValueError("only one member of a parallel mixer may keep pages of keys and values")
+        states = tuple((f"{name}.{s}", shape) for name, n in needs.items() for s, shape in n.states)
+        if any(n.state_shape is not None for n in needs.values()):
+            raise ValueError("members of a parallel mixer name their states")
+        base = paged[0] if paged else CacheNeed()
+        return CacheNeed(kind=base.kind, kv_heads=base.kv_heads, head_dim=base.head_dim, window=base.window,
+                         value_dim=base.value_dim, states=states)
+
+    def forward(self, x, ctx, cache):
+        ops = self.rt.ops
+        joint = ops.empty((x.shape[0], self.inner_width), self.rt.dtype)
+        for name, m in self.members.items():
+            m.write_inner(x, ctx, cache.member(name), joint, self.columns[name], self.scales[name])
+        return ops.linear(joint, self.w_o)

@@ -16,29 +16,36 @@ from .base import Part, PartSpec, Runtime, TensorSpec, register_part
 
 @register_part("norm", "rmsnorm")
 class RMSNorm(Part):
-    """params: ``width``, ``eps``; optional ``init`` ("ones" or "ones_jitter").  Tensor: ``weight`` [width]."""
+    """params: ``width``, ``eps``; optional ``offset`` (the stored weight is the factor minus this: 1.0 for
+    weights kept around zero) and ``init`` (how random-weights mode draws it).  Tensor: ``weight`` [width]."""
 
     def __init__(self, spec: PartSpec, runtime: Runtime):
         super().__init__(spec, runtime)
         self.width = int(spec.params["width"])
         self.eps = float(spec.params["eps"])
+        self.offset = float(spec.params.get("offset", 0.0))
         self.weight: Optional[torch.Tensor] = None
 
     def tensor_specs(self) -> Dict[str, TensorSpec]:
-        return {"weight": TensorSpec((self.width,), init=self.spec.params.get("init", "ones"))}
+        return {"weight": TensorSpec((self.width,), init=self.spec.params.get("init", "zeros" if self.offset else "ones"))}
 
     def load(self, tensors) -> None:
         self.weight = self._to_f32(tensors["weight"])  # norm weights stay 32-bit in every compute type
+        if self.offset:
+            self.weight += self.offset                 # the factor itself, added once in float32
 
     deferrable = True   # the product before this norm may prepare its input, the product after it finish it
 
-    def forward(self, x, residual, rows=None):
+    def forward(self, x, residual, rows=None, bias=None):
         """``x`` may be the prepared input that a product's epilogue made for this very norm (it has
         ``materialise``): the sum is in ``residual`` already, and it is handed on as it is for the
         next product to finish.  One made for another norm, or with ``rows``, only means that
-        nothing is left to add."""
+        nothing is left to add.  ``bias`` (float32 [width]) is added together with ``x``: the bias of
+        the projection that made ``x``, where that projection left it out."""
         if hasattr(x, "materialise"):
             if x.weight is self.weight and rows is None:
                 return x, residual
             x = None
+        if bias is not None:
+            return self.rt.ops.add_rmsnorm(x, residual, self.weight, self.eps, rows=rows, dtype=self.rt.dtype, bias=bias)
         return self.rt.ops.add_rmsnorm(x, residual, self.weight, self.eps, rows=rows, dtype=self.rt.dtype)

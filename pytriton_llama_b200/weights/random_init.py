@@ -3,7 +3,7 @@ configuration and a seed.
 
 lite_llama has no such mode (its layers start from torch's defaults,
 lite_llama/models/llama.py:22-24); matrices here are N(0, initializer_range), norm weights 1 or
-1 + N(0, 0.01).  Values are drawn on the CPU in float32 in the sorted order of the tensor names,
+1 + N(0, 0.01); a part may ask for zeros, 0.1 * N(0, 1) or a uniform range for a tensor of its own.  Values are drawn on the CPU in float32 in the sorted order of the tensor names,
 so that a folder depends on nothing but configuration, seed and stored element type.
 """
 from __future__ import annotations
@@ -30,6 +30,12 @@ def random_tensors(expected: Dict[str, TensorSpec], seed: int, std: float, dtype
             t = 1.0 + 0.01 * torch.randn(spec.shape, generator=gen, dtype=torch.float32)
         elif spec.init == "normal":
             t = std * torch.randn(spec.shape, generator=gen, dtype=torch.float32)
+        elif spec.init == "zeros":
+            t = torch.zeros(spec.shape, dtype=torch.float32)
+        elif spec.init == "zeros_jitter":
+            t = 0.1 * torch.randn(spec.shape, generator=gen, dtype=torch.float32)
+        elif spec.init == "uniform":
+            t = spec.lo + (spec.hi - spec.lo) * torch.rand(spec.shape, generator=gen, dtype=torch.float32)
         else:
             raise ValueError(f"tensor {name}: unknown init {spec.init!r}")
         out[name] = t.to(dtype)
@@ -52,6 +58,12 @@ def random_tensors_on_device(expected: Dict[str, TensorSpec], seed: int, std: fl
             t = 1.0 + 0.01 * torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device)
         elif spec.init == "normal":
             t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device).mul_(std)
+        elif spec.init == "zeros":
+            t = torch.zeros(spec.shape, dtype=torch.float32, device=device)
+        elif spec.init == "zeros_jitter":
+            t = torch.randn(spec.shape, generator=gen, dtype=torch.float32, device=device).mul_(0.1)
+        elif spec.init == "uniform":
+            t = torch.rand(spec.shape, generator=gen, dtype=torch.float32, device=device).mul_(spec.hi - spec.lo).add_(spec.lo)
         else:
             raise ValueError(f"tensor {name}: unknown init {spec.init!r}")
         out[name] = t.to(dtype)
@@ -59,7 +71,7 @@ def random_tensors_on_device(expected: Dict[str, TensorSpec], seed: int, std: fl
 
 
 def write_random_model(folder: Union[str, Path], config: Dict, seed: int = 0,
-                       dtype: torch.dtype = torch.bfloat16, norm_init: str = "ones",
+                       dtype: torch.dtype = torch.bfloat16, norm_init: Optional[str] = None,
                        std: Optional[float] = None) -> Path:
     """``config`` is the content of config.json (its ``architectures`` picks the model)."""
     from ..config.registry import resolve_architecture
@@ -68,7 +80,7 @@ def write_random_model(folder: Union[str, Path], config: Dict, seed: int = 0,
 
     arch = resolve_architecture(config)
     cfg = arch.config_from_dict(config)
-    spec = arch.spec_from_config(cfg, norm_init=norm_init)
+    spec = arch.spec_from_config(cfg, norm_init=norm_init) if norm_init is not None else arch.spec_from_config(cfg)
     model = DecoderModel(spec, Runtime(torch.device("cpu"), torch.float32, ops=None))
     expected = model.expected_tensors()
     tensors = random_tensors(expected, seed, spec.initializer_range if std is None else std, dtype)

@@ -24,13 +24,15 @@ class TorchOps:
     def embed(self, ids, table):
         return table[ids.long()].clone()
 
-    def add_rmsnorm(self, x, residual, weight, eps, rows=None, dtype=None):
+    def add_rmsnorm(self, x, residual, weight, eps, rows=None, dtype=None, bias=None):
         dtype = dtype or x.dtype
         s = None
         if residual is not None:
             s = residual.float()
         if x is not None:
             s = x.float() if s is None else s + x.float()
+        if bias is not None:
+            s = s + bias.float()
         if rows is not None:
             s = s[rows.long()]
         y = s * torch.rsqrt((s * s).mean(-1, keepdim=True) + eps) * weight.float()
@@ -131,3 +133,159 @@ class TorchOps:
 
     def bad_token_seen(self):
         return False
+
+    # ------------------------------------------------------------------ operators of the recurrent and chunked mixers
+    # (float64 inside, rounded once to the result's type; requests are walked one by one, tokens in order)
+    def embed_scaled(self, ids, table, scale, positions, base):
+        x = table[ids.long()].double() * scale
+        if base:
+            width = table.shape[1]
+            i = torch.arange(width // 2, dtype=torch.float64)
+            ang = positions.double()[:, None] * base ** (-2.0 * i / width)[None, :]
+            x[:, 0::2] += torch.sin(ang)
+            x[:, 1::2] += torch.cos(ang)
+        return x.float()
+
+    def softcap(self, logits, cap):
+        logits.copy_((cap * torch.tanh(logits.double() / cap)).float())
+
+    @staticmethod
+    def _requests(ctx):
+        qs = ctx.q_start.tolist()
+        for r in range(ctx.num_requests):
+            if qs[r + 1] > qs[r]:
+                yield qs[r], qs[r + 1], int(ctx.state_slot[r]), int(ctx.positions[qs[r]])
+
+    def causal_conv(self, x, column, channels, w, b, state, ctx, silu=True):
+        taps = w.shape[1]
+        out = torch.zeros((x.shape[0], channels), dtype=torch.float64)
+        for lo, hi, slot, pos0 in self._requests(ctx):
+            past = state[slot, :taps - 1].double() if pos0 > 0 else torch.zeros((taps - 1, channels), dtype=torch.float64)
+            if taps == 1:
+                past = past[:0]
+            seq = torch.cat([past, x[lo:hi, column:column + channels].double()], 0)
+            for k in range(taps):
+                out[lo:hi] += seq[k:k + hi - lo] * w[:, k].double()
+            if taps > 1:
+                state[slot, :taps - 1] = seq[-(taps - 1):].float()
+        if b is not None:
+            out += b.double()
+        if silu:
+            out = out * torch.sigmoid(out)
+        return out.to(x.dtype)
+
+    def selective_scan(self, xc, dt, dt_b, A, bc, D, xz, z_column, state, ctx):
+        inner, n = A.shape
+        y = torch.zeros((xc.shape[0], inner), dtype=torch.float64)
+        step = torch.nn.functional.softplus(dt.double() + dt_b.double(), threshold=30.0)
+        for lo, hi, slot, pos0 in self._requests(ctx):
+            S = state[slot].double() if pos0 > 0 else torch.zeros((inner, n), dtype=torch.float64)
+            for t in range(lo, hi):
+                x = xc[t].double()
+                S = torch.exp(step[t][:, None] * A.double()) * S + (step[t] * x)[:, None] * bc[t, :n].double()[None, :]
+                y[t] = S @ bc[t, n:2 * n].double() + D.double() * x
+            state[slot] = S.float()
+        z = xz[:, z_column:z_column + inner].double()
+        return (y * z * torch.sigmoid(z)).to(xc.dtype)
+
+    @staticmethod
+    def _page_views(cache, page, G, ps, d, dv):
+        flat = cache[page].reshape(-1)
+        return flat[:G * ps * d].view(G, ps, d), flat[G * ps * d:].view(G, ps, dv)
+
+    def kv_write_normed(self, qkv, bias, slots, cache, H, G, d, dv, page_size, eps):
+        for t in range(qkv.shape[0]):
+            s = int(slots[t])
+            if s < 0:
+                continue
+            row = qkv[t].double() + (bias.double() if bias is not None else 0.0)
+            k = row[H * d:(H + G) * d].view(G, d)
+            v = row[(H + G) * d:(H + G) * d + G * dv].view(G, dv)
+            if eps > 0:
+                v = v / torch.sqrt((v * v).mean(-1, keepdim=True) + eps)
+            page, off = divmod(s, page_size)
+            kp, vp = self._page_views(cache, page, G, page_size, d, dv)
+            kp[:, off] = k.to(cache.dtype)
+            vp[:, off] = v.to(cache.dtype)
+
+    def chunk_attention(self, qkv, bias, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, chunk,
+                        r1, r2, talk, out, column, out_scale):
+        group = H // G
+        for t in range(qkv.shape[0]):
+            r, p = int(tok_req[t]), int(positions[t])
+            if r < 0:
+                continue
+            lo = p // chunk * chunk if chunk else 0
+            keys = torch.arange(lo, p + 1)
+            q = qkv[t, :H * d].double()
+            if bias is not None:
+                q = q + bias[:H * d].double()
+            q = q.view(H, d)
+            ks, vs = [], []
+            for j in keys.tolist():
+                page = int(block_table[r, j // page_size])
+                assert page >= 0, "attention reads a page that was given back"
+                kp, vp = self._page_views(cache, page, G, page_size, d, dv)
+                ks.append(kp[:, j % page_size].double())
+                vs.append(vp[:, j % page_size].double())
+            k, v = torch.stack(ks), torch.stack(vs)                  # [n, G, d], [n, G, dv]
+            w = torch.zeros((H, len(keys)), dtype=torch.float64)
+            for h in range(H):
+                sc = (k[:, h // group] @ q[h]) * scale
+                if r1 is not None:
+                    sc = sc - float(r1[h]) * torch.log1p(float(r2[h]) * (p - keys).double())
+                w[h] = torch.softmax(sc, 0)
+            if talk is not None:
+                w = talk.double() @ w
+            o = torch.stack([w[h] @ v[:, h // group] for h in range(H)]).reshape(-1) * out_scale
+            out[t, column:column + H * dv] = o.to(out.dtype)
+
+    def gated_delta_rule(self, qkv, ba, rate, dt_bias, S_all, ctx, H, G, d, dv, unit_eps, q_scale):
+        T = qkv.shape[0]
+        o = torch.zeros((T, H, dv), dtype=torch.float64)
+        x = qkv.double()
+        q = x[:, :G * d].view(T, G, d)
+        k = x[:, G * d:2 * G * d].view(T, G, d)
+        v = x[:, 2 * G * d:].view(T, H, dv)
+        q = q / torch.sqrt((q * q).sum(-1, keepdim=True) + unit_eps) * q_scale
+        k = k / torch.sqrt((k * k).sum(-1, keepdim=True) + unit_eps)
+        beta = torch.sigmoid(ba[:, :H].double())
+        decay = torch.exp(-rate.double() * torch.nn.functional.softplus(ba[:, H:].double() + dt_bias.double(), threshold=30.0))
+        for lo, hi, slot, pos0 in self._requests(ctx):
+            S = S_all[slot].double() if pos0 > 0 else torch.zeros((H, d, dv), dtype=torch.float64)
+            for t in range(lo, hi):
+                for h in range(H):
+                    c = h // (H // G)
+                    Sh = decay[t, h] * S[h]
+                    u = beta[t, h] * (v[t, h] - Sh.T @ k[t, c])
+                    S[h] = Sh + torch.outer(k[t, c], u)
+                    o[t, h] = S[h].T @ q[t, c]
+            S_all[slot] = S.float()
+        return o.reshape(T, H * dv).float()
+
+    def gated_head_norm(self, o, weight, eps, gate, gate_column, H, dv, out, column, scale):
+        T = o.shape[0]
+        x = o.double().view(T, H, dv)
+        x = x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * weight.double()
+        g = gate[:, gate_column:gate_column + H * dv].double()
+        out[:, column:column + H * dv] = (x.reshape(T, H * dv) * g * torch.sigmoid(g) * scale).to(out.dtype)
+
+    def clamped_glu(self, gu, bias, limit, alpha, up_shift):
+        inter = gu.shape[1] // 2
+        x = gu.double() + (bias.double() if bias is not None else 0.0)
+        g = torch.clamp(x[:, :inter], max=limit)
+        u = torch.clamp(x[:, inter:], -limit, limit)
+        return (g * torch.sigmoid(alpha * g) * (u + up_shift)).to(gu.dtype)
+
+    def token_side(self, residual, x, bias, tokens, table, column, dim, w_gate, w_proj, norm_w, eps):
+        s = residual.double()
+        if x is not None:
+            s = s + x.double()
+        if bias is not None:
+            s = s + bias.double()
+        e = table[tokens.long(), column:column + dim].double()
+        z = s @ w_gate.double().T
+        g = 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3))) * e
+        y = g @ w_proj.double().T
+        s = s + y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * norm_w.double()
+        residual.copy_(s.float())
