@@ -32,7 +32,7 @@ class RMSNorm(Part):
     def load(self, tensors) -> None:
         self.weight = self._to_f32(tensors["weight"])  # norm weights stay 32-bit in every compute type
         if self.offset:
-            self.weight += self.offset                 # the factor itself, added once in float32
+            self.weight = self.weight + self.offset    # the factor itself, added once in float32 (a new tensor: the file's is read-only)
 
     deferrable = True   # the product before this norm may prepare its input, the product after it finish it
 

@@ -1,0 +1,359 @@
+"""The Tibepel decoder on the GPU: every new kernel against the plain PyTorch statement of its operator
+(tests/torch_ops.py), attention inputs made so that one key stands out at the edges of blocks and pages, and the
+engine -- whole prompts, decoding, portions, mixed batches, generation -- against tests/plain_tibepel.py."""
+import json
+import math
+import random
+import subprocess
+import sys
+from pathlib import Path
+from types import SimpleNamespace
+
+import pytest
+import torch
+
+import plain_tibepel as plain
+import traces
+from conftest import ROOT, random_tokens
+from torch_ops import TorchOps
+
+pytestmark = pytest.mark.gpu
+DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL32 = 2e-4
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from pytriton_llama_b200.ops.cuda import CudaOps
+    return CudaOps(torch.device("cuda:0"))
+
+
+def _ctx(q_lens, starts, slots, device):
+    """A step of requests that bring q_lens[r] tokens after starts[r] earlier ones, their states in slots[r]."""
+    t = lambda v: torch.tensor(v, dtype=torch.int32, device=device)
+    q_start = [0]
+    for n in q_lens:
+        q_start.append(q_start[-1] + n)
+    return SimpleNamespace(num_requests=len(q_lens), num_tokens=q_start[-1], q_start=t(q_start), state_slot=t(slots),
+                           tok_req=t([r for r, n in enumerate(q_lens) for _ in range(n)]),
+                           positions=t([s + i for s, n in zip(starts, q_lens) for i in range(n)]))
+
+
+def _both(ops, fn, tensors, ctx_args, dtype):
+    """Runs fn(ops, tensors, ctx) with the CUDA operators and with the plain ones on copies; returns both results."""
+    dev = {k: (v.cuda() if isinstance(v, torch.Tensor) else v) for k, v in tensors.items()}
+    cpu = {k: (v.clone() if isinstance(v, torch.Tensor) else v) for k, v in tensors.items()}
+    got = fn(ops, dev, _ctx(*ctx_args, "cuda:0"))
+    ref = fn(TorchOps(), cpu, _ctx(*ctx_args, "cpu"))
+    torch.cuda.synchronize()
+    return got, ref, dev, cpu
+
+
+def _close(got, ref, dtype, what, scale=None):
+    got, ref = got.double().cpu(), ref.double()
+    assert torch.isfinite(got).all(), what
+    scale = scale or max(1.0, float(ref.abs().max()))
+    tol = 2e-5 if dtype == "float32" else 1.2e-2      # bfloat16: both sides round their result once, a last place apart at most
+    assert (got - ref).abs().max() <= tol * scale, f"{what}: {(got - ref).abs().max():.3e} of {scale:.2f}"
+
+
+STEP = ([5, 1, 2, 9], [0, 17, 3, 0], [2, 0, 3, 1])      # a fresh portion, a single token, two tokens of a running request, a fresh one
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("taps,channels", [(4, 40), (2, 129), (5, 8), (1, 16)])
+def test_causal_conv_and_its_state(ops, dtype, taps, channels):
+    g = torch.Generator().manual_seed(taps * 100 + channels)
+    T = sum(STEP[0])
+    tensors = {"x": torch.randn(T, channels + 7, generator=g).to(DTYPES[dtype]), "w": torch.randn(channels, taps, generator=g),
+               "b": torch.randn(channels, generator=g), "state": torch.randn(5, max(taps - 1, 1), channels, generator=g)}
+    run = lambda o, t, ctx: o.causal_conv(t["x"], 3, channels, t["w"], t["b"], t["state"], ctx, silu=True)
+    got, ref, dev, cpu = _both(ops, run, tensors, STEP, dtype)
+    _close(got, ref, dtype, "outputs")
+    _close(dev["state"], cpu["state"], "float32", "state after the step")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("inner,n", [(40, 5), (17, 16), (64, 24), (33, 70)])
+def test_selective_scan(ops, dtype, inner, n):
+    g = torch.Generator().manual_seed(inner + n)
+    T = sum(STEP[0])
+    dt = DTYPES[dtype]
+    tensors = {"xc": torch.randn(T, inner, generator=g).to(dt), "dt": torch.randn(T, inner, generator=g),
+               "dt_b": torch.randn(inner, generator=g) - 1, "A": -torch.exp(torch.randn(inner, n, generator=g)),
+               "bc": torch.randn(T, 2 * n, generator=g).to(dt), "D": torch.randn(inner, generator=g),
+               "xz": torch.randn(T, 2 * inner, generator=g).to(dt), "state": torch.randn(5, inner, n, generator=g)}
+    run = lambda o, t, ctx: o.selective_scan(t["xc"], t["dt"], t["dt_b"], t["A"], t["bc"], t["D"], t["xz"], inner, t["state"], ctx)
+    got, ref, dev, cpu = _both(ops, run, tensors, STEP, dtype)
+    _close(got, ref, dtype, "outputs")
+    _close(dev["state"], cpu["state"], "float32", "state after the step")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,d,dv", [(4, 2, 8, 16), (1, 1, 40, 24), (6, 6, 32, 64), (2, 1, 100, 9), (3, 3, 130, 20)])
+def test_gated_delta_rule(ops, dtype, H, G, d, dv):
+    g = torch.Generator().manual_seed(H * 1000 + d)
+    T = sum(STEP[0])
+    tensors = {"qkv": torch.randn(T, 2 * G * d + H * dv, generator=g).to(DTYPES[dtype]), "ba": torch.randn(T, 2 * H, generator=g),
+               "rate": torch.exp(torch.randn(H, generator=g)), "dt_bias": torch.randn(H, generator=g),
+               "S": torch.randn(5, H, d, dv, generator=g)}
+    run = lambda o, t, ctx: o.gated_delta_rule(t["qkv"], t["ba"], t["rate"], t["dt_bias"], t["S"], ctx, H, G, d, dv, 1e-6, d ** -0.5)
+    got, ref, dev, cpu = _both(ops, run, tensors, STEP, dtype)
+    _close(got, ref, "float32", "read-outs", scale=max(1.0, float(ref.abs().max())) * 5)
+    _close(dev["S"], cpu["S"], "float32", "state after the step", scale=max(1.0, float(cpu["S"].abs().max())) * 5)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_row_wise_operators(ops, dtype):
+    g = torch.Generator().manual_seed(3)
+    dt = DTYPES[dtype]
+    T, W, V, dim, H, dv, F = 11, 72, 50, 6, 3, 20, 52
+    ids = torch.randint(0, V, (T,), generator=g, dtype=torch.int32)
+    pos = torch.tensor([0, 1, 2, 3, 900, 901, 65, 4000, 7, 8, 9], dtype=torch.int32)
+    table = torch.randn(V, W, generator=g).to(dt)
+    got = ops.embed_scaled(ids.cuda(), table.cuda(), 3.5, pos.cuda(), 10000.0)
+    ref = table[ids.long()].double() * 3.5 + torch.cat([plain.position_vector(4001, W)[int(p)][None] for p in pos])
+    _close(got, ref, "float32", "scaled embedding with positions")
+    # the add into the stream with a bias, and the norm whose weight is stored around zero
+    x, res, w, b = torch.randn(T, W, generator=g).to(dt), torch.randn(T, W, generator=g), torch.randn(W, generator=g), torch.randn(W, generator=g)
+    res_dev = res.cuda()
+    y, _ = ops.add_rmsnorm(x.cuda(), res_dev, (w + 1).cuda(), 1e-5, dtype=dt, bias=b.cuda())
+    s = res.double() + x.double() + b.double()
+    _close(res_dev, s, "float32", "stream after the add")
+    _close(y, plain.norm_around_zero(s, w.double(), 1e-5), dtype, "normed")
+    gu, bias = torch.randn(T, 2 * F, generator=g).to(dt) * 2, torch.randn(2 * F, generator=g)
+    _close(ops.clamped_glu(gu.cuda(), bias.cuda(), 1.5, 1.702, 1.0), TorchOps().clamped_glu(gu, bias, 1.5, 1.702, 1.0), dtype, "clamped glu")
+    side, wg, wp, nw = torch.randn(V, 4 * dim, generator=g).to(dt), torch.randn(dim, W, generator=g).to(dt) / 8, torch.randn(W, dim, generator=g).to(dt), torch.randn(W, generator=g)
+    res_dev, res_cpu = res.cuda(), res.clone()
+    ops.token_side(res_dev, x.cuda(), b.cuda(), ids.cuda(), side.cuda(), 2 * dim, dim, wg.cuda(), wp.cuda(), nw.cuda(), 1e-5)
+    TorchOps().token_side(res_cpu, x, b, ids, side, 2 * dim, dim, wg, wp, nw, 1e-5)
+    _close(res_dev, res_cpu, "float32", "stream after the side term", scale=20.0 if dtype == "float32" else 2000.0)
+    o, nwt, gate = torch.randn(T, H * dv, generator=g), torch.randn(dv, generator=g), torch.randn(T, 5 + H * dv, generator=g).to(dt)
+    out_dev, out_cpu = torch.zeros(T, 4 + H * dv, dtype=dt, device="cuda"), torch.zeros(T, 4 + H * dv, dtype=dt)
+    ops.gated_head_norm(o.cuda(), nwt.cuda(), 1e-5, gate.cuda(), 5, H, dv, out_dev, 4, 0.6)
+    TorchOps().gated_head_norm(o, nwt, 1e-5, gate, 5, H, dv, out_cpu, 4, 0.6)
+    _close(out_dev, out_cpu, dtype, "gated head norm")
+    logits = torch.randn(5, 33, generator=g) * 40
+    dev = logits.cuda()
+    ops.softcap(dev, 30.0)
+    _close(dev, 30 * torch.tanh(logits.double() / 30), "float32", "capped logits")
+
+
+def _attention_case(o, device, dtype, H, G, d, dv, page, chunk, ctx_len, q_len, loud_key, rng):
+    """One request of ctx_len tokens whose last q_len are this step's queries.  Every key is noise except ``loud_key``,
+    which all heads of the last query match strongly.  Returns the last query's output [H, dv] and the values [ctx_len, G, dv]."""
+    dt = DTYPES[dtype]
+    g = torch.Generator().manual_seed(rng)
+    pages = -(-ctx_len // page)
+    order = torch.randperm(pages + 3, generator=g)[:pages].tolist()          # scattered pages
+    table = torch.full((1, pages + 2), -1, dtype=torch.int32)
+    table[0, :pages] = torch.tensor(order, dtype=torch.int32)
+    cache = torch.zeros(pages + 3, G * page * (d + dv), dtype=dt)
+    direction = torch.randn(d, generator=g)
+    direction = direction / direction.norm()
+    rows = 0.1 * torch.randn(ctx_len, H * d + G * (d + dv), generator=g)
+    rows[:, (H + G) * d:] = torch.randn(ctx_len, G * dv, generator=g)
+    if loud_key is not None:
+        rows[loud_key, H * d:(H + G) * d] = (direction * 30).repeat(G)
+    rows[ctx_len - 1, :H * d] = (direction * 30).repeat(H)
+    rows = rows.to(dt)
+    slots = torch.tensor([order[p // page] * page + p % page for p in range(ctx_len)], dtype=torch.int32)
+    to = lambda t: t.to(device)
+    cache, rows_d = to(cache), to(rows)
+    o.kv_write_normed(rows_d, None, to(slots), cache, H, G, d, dv, page, 0.0)
+    first = ctx_len - q_len
+    out = torch.zeros(q_len, H * dv + 2, dtype=dt, device=device)
+    o.chunk_attention(rows_d[first:].contiguous(), None, cache, to(table), to(torch.zeros(q_len, dtype=torch.int32)),
+                      to(torch.arange(first, ctx_len, dtype=torch.int32)), H, G, d, dv, page, 1.0, chunk, None, None, None, out, 1, 1.0)
+    return out[-1, 1:1 + H * dv].float().cpu().view(H, dv), rows[:, (H + G) * d:].float().view(ctx_len, G, dv)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("q_len", [1, 7])
+def test_a_key_that_stands_out_is_seen_inside_its_block_only(ops, dtype, q_len):
+    H, G, d, dv, page, chunk = 4, 2, 32, 16, 16, 24
+    for ctx_len, key, seen in [(24, 0, True), (25, 23, False), (25, 24, True), (47, 24, True), (48, 23, False), (49, 47, False),
+                               (49, 48, True), (40, 31, True), (40, 32, True), (313, 311, False), (313, 312, True), (335, 312, True)]:
+        if ctx_len - q_len < 0 or (q_len > 1 and ctx_len < q_len):
+            continue
+        out, values = _attention_case(ops, "cuda:0", dtype, H, G, d, dv, page, chunk, ctx_len, q_len, key, rng=ctx_len)
+        quiet, _ = _attention_case(ops, "cuda:0", dtype, H, G, d, dv, page, chunk, ctx_len, q_len, None, rng=ctx_len)
+        for h in range(H):
+            if seen:      # the weight of the loud key is 1 to within e^-800
+                assert (out[h] - values[key, h // (H // G)]).abs().max() < 2e-2, (ctx_len, key, h)
+            else:         # nothing changes when a key outside the block is made loud
+                assert (out[h] - quiet[h]).abs().max() < 1e-6, (ctx_len, key, h)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H,G,d,dv,page,chunk", [(4, 2, 16, 24, 4, 8), (6, 2, 32, 16, 16, 24), (3, 3, 20, 20, 8, 0), (8, 1, 64, 64, 16, 64)])
+def test_chunk_attention_with_bias_and_mixed_heads(ops, dtype, H, G, d, dv, page, chunk):
+    g = torch.Generator().manual_seed(H * 10 + d)
+    dt = DTYPES[dtype]
+    q_lens, starts = [9, 1, 30, 1], [0, 40, 5, 0]
+    T = sum(q_lens)
+    ctx = [s + n for s, n in zip(starts, q_lens)]
+    pages_per = [-(-c // page) for c in ctx]
+    order = torch.randperm(sum(pages_per) + 2, generator=g).tolist()
+    table = torch.full((4, max(pages_per) + 1), -1, dtype=torch.int32)
+    cache = (torch.randn(sum(pages_per) + 2, G * page * (d + dv), generator=g)).to(dt)      # earlier tokens' keys and values: noise
+    at, slots = 0, []
+    for r in range(4):
+        table[r, :pages_per[r]] = torch.tensor(order[at:at + pages_per[r]], dtype=torch.int32)
+        at += pages_per[r]
+        slots += [int(table[r, p // page]) * page + p % page for p in range(starts[r], ctx[r])]
+    t = {"qkv": torch.randn(T, H * d + G * (d + dv), generator=g).to(dt), "bias": torch.randn(H * d + G * (d + dv), generator=g) * 0.3,
+         "cache": cache, "table": table, "slots": torch.tensor(slots, dtype=torch.int32), "r1": torch.rand(H, generator=g),
+         "r2": torch.rand(H, generator=g) + 0.1, "talk": torch.randn(H, H, generator=g), "out": torch.zeros(T, H * dv + 3, dtype=dt)}
+
+    def run(o, t, c):
+        o.kv_write_normed(t["qkv"], t["bias"], t["slots"], t["cache"], H, G, d, dv, page, 1e-5)
+        o.chunk_attention(t["qkv"], t["bias"], t["cache"], t["table"], c.tok_req, c.positions, H, G, d, dv, page, 0.2, chunk,
+                          t["r1"], t["r2"], t["talk"], t["out"], 2, 0.7)
+        return t["out"]
+    got, ref, dev, cpu = _both(ops, run, t, (q_lens, starts, [0, 1, 2, 3]), dtype)
+    _close(dev["cache"], cpu["cache"], dtype, "cache after the write")
+    _close(got, ref, dtype, "outputs", scale=max(1.0, float(ref.abs().max())) * (1 if dtype == "float32" else 3))
+
+
+# ---------------------------------------------------------------------------- the engine
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    made = {}
+
+    def get(name, dtype):
+        if (name, dtype) not in made:
+            folder = tmp_path_factory.mktemp(f"tibepel_{name}_{dtype}")
+            plain.write_model(folder, plain.TINY[name], 11, DTYPES[dtype])
+            made[(name, dtype)] = folder
+        return made[(name, dtype)]
+    return get
+
+
+def _engine(folder, dtype, page, pages, max_seq_len=512, slots=4, **extra):
+    from pytriton_llama_b200.config import EngineConfig
+    from pytriton_llama_b200.engine.engine import Engine
+    return Engine(folder, EngineConfig(dtype=dtype, page_size=page, max_gpu_num_blocks=pages, max_seq_len=max_seq_len,
+                                       max_num_seqs=slots, **extra), device="cuda:0")
+
+
+def _reference(folder, seqs):
+    from pytriton_llama_b200.weights import read_folder
+    cfg = json.loads((folder / "config.json").read_text())
+    W = read_folder(folder)
+    return {r: plain.forward(cfg, W, s) for r, s in seqs.items()}
+
+
+def _assert_logits(got, ref, dtype, what):
+    diff = (got.double().cpu() - ref).abs()
+    if dtype == "float32":
+        assert diff.max() < TOL32, f"{what}: {diff.max():.3e}"
+    else:
+        centred = (got.double().cpu() - ref) - (got.double().cpu() - ref).mean(-1, keepdim=True)
+        rms = centred.pow(2).mean(-1).sqrt() / ref.std()
+        # Rounding alone gives 0.01 to 0.015 of the logits' spread in the mean over rows with these weights, and up to
+        # 0.16 in single rows (a clamp or a sharp softmax next to its edge).  A fault of a mechanism shows in float32,
+        # where the bound is 2e-4; here the bfloat16 kernels must stay at the level of rounding.
+        assert rms.max() < 0.3 and rms.mean() < 0.03 + 0.07 * (rms.numel() < 4), \
+            f"{what}: worst row {rms.max():.3f}, mean {rms.mean():.3f} of the logits' spread"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name,page", [("P", 4), ("Q", 16)])
+def test_every_cut_gives_the_whole_sequence_logits(folders, dtype, name, page):
+    folder = folders(name, dtype)
+    vocab = plain.TINY[name]["vocab"]
+    seqs = {f"r{i}": random_tokens(n, vocab, 700 + i) for i, n in enumerate([1, 9, 33, 130, 12, 27, 64])}
+    ref = _reference(folder, seqs)
+    for family in (traces.whole, traces.prefill_then_decode, traces.portions, traces.mixed):
+        steps = family(seqs)
+        pages = -(-traces.max_live_tokens(steps, 16) // page)
+        eng = _engine(folder, dtype, page, pages)
+        got = traces.replay(eng, steps)
+        for r in seqs:
+            _assert_logits(got[r], ref[r], dtype, f"{family.__name__} {r}")
+        eng.check_device_status()
+        assert eng.cache.free_slots() == 4 and all(eng.cache.free_pages(g) == pages for g in eng._paged_groups())
+
+
+@pytest.mark.parametrize("seed", [1, 2])
+def test_random_traces_in_float32(folders, seed):
+    folder = folders("Q", "float32")
+    rng = random.Random(seed)
+    seqs = {f"q{i}": random_tokens(rng.randint(1, 200), 130, 900 + 10 * seed + i) for i in range(7)}
+    ref = _reference(folder, seqs)
+    steps = traces.random_trace(seqs, rng)
+    eng = _engine(folder, "float32", 16, -(-traces.max_live_tokens(steps, 16) // 16))
+    got = traces.replay(eng, steps)
+    for r in seqs:
+        want = traces.wanted_positions(steps, r)
+        if want:
+            _assert_logits(got[r], ref[r][want], "float32", f"random trace {seed} {r}")
+
+
+def test_batch_does_not_change_a_request(folders):
+    from pytriton_llama_b200.engine.engine import StepEntry
+    folder = folders("P", "float32")
+    seqs = {"long": random_tokens(61, 96, 7), "short": random_tokens(3, 96, 8), "one": random_tokens(1, 96, 9)}
+    alone = {r: traces.replay(_engine(folder, "float32", 4, 40), traces.whole({r: s}))[r] for r, s in seqs.items()}
+    out = _engine(folder, "float32", 4, 40).step([StepEntry(r, s, list(range(len(s)))) for r, s in seqs.items()])
+    at = 0
+    for r, s in seqs.items():
+        assert (out.logits[at:at + len(s)].cpu() - alone[r]).abs().max() < 2e-5, r
+        at += len(s)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(folders, dtype):
+    from pytriton_llama_b200.engine.engine import StepEntry
+    folder = folders("Q", dtype)
+    toks = random_tokens(400, 130, 21)
+    ref = _reference(folder, {"a": toks})["a"]
+    eng = _engine(folder, dtype, 16, 8)           # 8 pages for 400 tokens: the blocks' pages come back as decoding goes on
+    rows = [eng.step([StepEntry("a", toks[:3], [0, 1, 2])]).logits] + [eng.step([StepEntry("a", [t], [0])]).logits for t in toks[3:]]
+    _assert_logits(torch.cat(rows), ref, dtype, "400 tokens, one by one")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_generation_through_the_scheduler(folders, dtype):
+    from pytriton_llama_b200 import LLM, EngineConfig, SamplingParams
+    folder = folders("P", dtype)
+    prompts = [random_tokens(n, 96, 40 + i) for i, n in enumerate([5, 23, 2, 14, 9, 31])]
+    cfg = EngineConfig(dtype=dtype, page_size=4, max_gpu_num_blocks=48, max_seq_len=64, max_num_seqs=3, max_batched_tokens=16)
+    outs = LLM(folder, cfg).generate(prompts, SamplingParams(temperature=0.0, max_gen_len=8))
+    for p, o in zip(prompts, outs):
+        assert len(o) == 8
+        logits = _reference(folder, {"x": p + o})["x"]
+        slack = 1e-3 if dtype == "float32" else 0.05 * float(logits.std())
+        for i, tok in enumerate(o):
+            row = logits[len(p) + i - 1]
+            assert row[tok] >= row.max() - slack, (i, tok, int(row.argmax()))
+
+
+def test_trace_runner_and_command_line(folders, tmp_path):
+    folder = folders("P", "bfloat16")
+    seqs = {"a": random_tokens(40, 96, 1), "b": random_tokens(13, 96, 2)}
+    steps = traces.mixed(seqs)
+    lines = "\n".join(json.dumps(s) for s in steps) + "\n"
+    for dtype in ("bfloat16", "float32"):
+        out = tmp_path / dtype
+        proc = subprocess.run([str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
+                               "--max-tokens", str(traces.max_live_tokens(steps))], input=lines, text=True, capture_output=True,
+                              timeout=900)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert [l for l in proc.stdout.splitlines() if l.startswith("done ")] == [f"done {s['step']}" for s in steps]
+        ref = _reference(folder, seqs)
+        fed = {r: 0 for r in seqs}
+        for s in steps:
+            rows = torch.frombuffer(bytearray((out / f"{s['step']}.f32").read_bytes()), dtype=torch.float32).view(-1, 96)
+            at = 0
+            for e in s["entries"]:
+                for w in e["want"]:
+                    _assert_logits(rows[at][None], ref[e["id"]][fed[e["id"]] + w][None], dtype, f"{dtype} step {s['step']}")
+                    at += 1
+                fed[e["id"]] += len(e["tokens"])
+    proc = subprocess.run([sys.executable, str(ROOT / "cli.py"), "--checkpoints_dir", str(folder), "--temperature", "0",
+                           "--max_gen_len", "5", "--max_seq_len", "64", "--page_size", "4", "--prompt_ids", "3", "1", "4", "1", "5"],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert len(proc.stdout.split()) == 5

@@ -160,9 +160,10 @@ class TorchOps:
         taps = w.shape[1]
         out = torch.zeros((x.shape[0], channels), dtype=torch.float64)
         for lo, hi, slot, pos0 in self._requests(ctx):
-            past = state[slot, :taps - 1].double() if pos0 > 0 else torch.zeros((taps - 1, channels), dtype=torch.float64)
-            if taps == 1:
-                past = past[:0]
+            past = state[slot, :taps - 1].double().clone() if taps > 1 else torch.zeros((0, channels), dtype=torch.float64)
+            for j in range(taps - 1):            # entry j is the input at position pos0 - (taps - 1) + j: nothing before position 0
+                if pos0 - (taps - 1) + j < 0:
+                    past[j] = 0
             seq = torch.cat([past, x[lo:hi, column:column + channels].double()], 0)
             for k in range(taps):
                 out[lo:hi] += seq[k:k + hi - lo] * w[:, k].double()
