@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the engine on one B200, Llama-3.2-1B shape, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --family tibepel      # another workload: the Tibepel decoder beside a Llama of equal size
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and context 4096, timed on
 the device with CUDA events around exactly K decode steps (a step = the engine's step function for
@@ -152,6 +153,131 @@ def reference_arm(args) -> int:
     return 0
 
 
+# ---------------------------------------------------------------------------- the Tibepel decoder beside a Llama of equal size
+def _tibepel(width, layers, ff, vocab):
+    """A Tibepel of sizes that resemble a real model's layers: every fourth layer a selective scan (inner = 2 width,
+    16 states), the others attention in blocks of 256 positions (head size 128, 4 query heads per kv head) beside a
+    gated delta rule (key size 128, value size 128)."""
+    heads = width // 128
+    scan = {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}
+    par = {"left": {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "mask": {"size": 256}, "scale": 128 ** -0.5},
+           "right": {"heads": heads, "kv_heads": heads, "dim": 128, "vdim": 128, "conv": 4}, "left_scale": 0.6, "right_scale": 0.5}
+    mlp = {"kind": "dense", "ff": ff, "limit": 7.0}
+    return {"architecture": "Tibepel", "vocab": vocab, "width": width, "embedding": {"scale": width ** 0.5}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "token_side": {"dim": 64},
+            "layers": [{"type": "mamba1" if i % 4 == 0 else "parallel", "mixer": scan if i % 4 == 0 else par, "mlp": mlp}
+                       for i in range(layers)]}
+
+
+def family_bench(args) -> int:
+    """``--family tibepel``: prefill (one step of 2,048 prompt tokens) and decode (8 requests at 1,024 tokens, a step
+    with its sampling kernel) of the Tibepel decoder and of a Llama decoder of the same width, depth, feed-forward size
+    and vocabulary, on random weights, timed with CUDA events after warm-up; then one timed step of each kind with
+    every operator bracketed by events, for the milliseconds by class of kernels.  One JSON line."""
+    import torch
+    from pytriton_llama_b200.config import EngineConfig
+    from pytriton_llama_b200.engine.engine import Engine, StepEntry
+
+    peaks, peak_kind = load_peaks()
+    sizes = [(1024, 8, 4096), (2048, 8, 8192)] if not args.family_sizes else \
+        [tuple(int(v) for v in item.split("x")) for item in args.family_sizes.split(",")]
+    vocab, prompt_len, batch, context = 32000, PREFILL_TOKENS, 8, 1024
+    W, K = max(3, args.warmup), args.steps
+    gen = torch.Generator().manual_seed(0)
+    toks = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
+    rows = []
+    for width, layers, ff in sizes:
+        models = {"tibepel": _tibepel(width, layers, ff, vocab),
+                  "llama": dict(_llama(layers, width, width // 128, max(1, width // 512), 128, ff, 32.0, False), vocab_size=vocab)}
+        row = {"width": width, "layers": layers, "ff": ff, "vocab": vocab}
+        for name, cfg in models.items():
+            pages = (batch + 1) * (-(-(context + K + W + 8) // 16)) + 2 * (-(-prompt_len // 16))
+            ecfg = EngineConfig(dtype=args.dtype, page_size=16, max_gpu_num_blocks=pages, max_seq_len=max(prompt_len, context + K + W + 8),
+                                max_num_seqs=batch + 1, max_batched_tokens=prompt_len, compiled_model=not args.no_graph, seed=0)
+            engine = Engine(None, ecfg, model_config=cfg, random_seed=0)
+            ops, dev = engine.ops, engine.device
+
+            def timed(fn, reps):
+                torch.cuda.synchronize(dev)
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record()
+                for _ in range(reps):
+                    fn()
+                b.record()
+                torch.cuda.synchronize(dev)
+                return a.elapsed_time(b) / reps
+
+            prompt = toks(prompt_len)
+
+            def prefill():
+                engine.step([StepEntry("p", prompt, [prompt_len - 1])])
+                engine.finish("p")
+            for _ in range(3):
+                prefill()
+            prefill_ms = statistics.median(timed(prefill, 1) for _ in range(5))
+            reqs = [f"d{i}" for i in range(batch)]
+            for r in reqs:
+                engine.step([StepEntry(r, toks(context), [])])
+            feed = [[t] for t in toks(batch)]
+
+            def decode():
+                out = engine.step([StepEntry(r, f, [0]) for r, f in zip(reqs, feed)], own_logits=False)
+                ops.sample(out.logits, None, None, None)
+            for _ in range(W):
+                decode()
+            before = ops.launches
+            decode_ms = timed(decode, K)
+            launches = (ops.launches - before) // K
+            # by class of kernels: the same two steps once more, every operator between two events (uncaptured)
+            engine.config.timing = True
+            ops.enable_timing()
+            out = engine.step([StepEntry("p", prompt, [prompt_len - 1])])
+            engine.finish("p")
+            prefill_classes = out.kernel_ms
+            decode_classes = engine.step([StepEntry(r, f, [0]) for r, f in zip(reqs, feed)]).kernel_ms
+            params = sum(t.numel() for t in _tensors_of(engine))
+            row[name] = {"prefill_tokens_per_s": round(prompt_len / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+                         "decode_tokens_per_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),
+                         "decode_launches_per_step": int(launches), "weights_gb": round(params * (4 if args.dtype == "float32" else 2) / 1e9, 3),
+                         "decode_hbm_frac": round(params * (4 if args.dtype == "float32" else 2) / (decode_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
+                         "prefill_ms_by_class": {k: round(v, 3) for k, v in sorted((prefill_classes or {}).items())},
+                         "decode_ms_by_class": {k: round(v, 4) for k, v in sorted((decode_classes or {}).items())}}
+            engine.check_device_status()
+            del engine
+            torch.cuda.empty_cache()
+        rows.append(row)
+    print(json.dumps({"metric": "family_tokens_per_s", "family": "tibepel", "beside": "llama of equal width, depth, feed-forward and vocabulary",
+                      "dtype": args.dtype, "data": "synthetic", "n_gpus": 1, "steps": K, "warmup": W,
+                      "workload": {"prefill_tokens": prompt_len, "decode_batch": batch, "decode_context": context},
+                      "peaks": dict(peaks, kind=peak_kind), "sizes": rows}))
+    return 0
+
+
+def _tensors_of(engine):
+    """Every weight tensor the engine's model holds on the device (counted once)."""
+    import torch
+    seen, out = set(), []
+
+    def visit(obj, depth=0):
+        if isinstance(obj, torch.Tensor):
+            if obj.data_ptr() not in seen and obj.is_cuda:
+                seen.add(obj.data_ptr())
+                out.append(obj)
+        elif isinstance(obj, dict) and depth < 4:
+            for v in obj.values():
+                visit(v, depth + 1)
+        elif hasattr(obj, "__dict__") and depth < 4 and type(obj).__module__.startswith("pytriton_llama_b200.parts"):
+            for v in vars(obj).values():
+                visit(v, depth + 1)
+    model = engine.model
+    for t in (model.embedding, model.lm_head):
+        visit(t)
+    visit(engine.runtime.shared)
+    for part in model.blocks + [model.final_norm]:
+        visit(part)
+    return out
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -164,6 +290,9 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=None, help="decode batch (default: 8; 32 for 3b; 64 for 8b)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--points", default=None, help="extra decode batch sizes, comma separated ('' for none)")
+    ap.add_argument("--family", default=None, choices=["tibepel"],
+                    help="another workload: this decoder beside a Llama of equal size, prefill and decode (own JSON line)")
+    ap.add_argument("--family-sizes", default=None, help="with --family: WIDTHxLAYERSxFF[,...] (default 1024x8x4096,2048x8x8192)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--no-prefill", action="store_true", help="skip the 2,048-token prefill measurement (profiling runs)")
@@ -173,6 +302,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.family:
+        return family_bench(args)
     shape = SHAPES[args.shape]
     args.batch = args.batch or shape["batch"]
     args.points = shape["points"] if args.points is None else args.points

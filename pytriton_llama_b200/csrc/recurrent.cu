@@ -1,7 +1,8 @@
 // Kernels of the mixers that carry a per-request state of fixed size from step to step: the short
 // causal convolution, the selective scan, the gated delta rule, and the per-head norm with an output
-// gate.  States are float32 arrays [slots, ...]; a request's slot is state_slot[r], and a request
-// whose first token of the step has position 0 starts from zeros whatever its slot holds.  A step's
+// gate.  States are float32 arrays [slots, ...]; a request's slot is state_slot[r] (negative: a padding
+// row of a captured step, skipped), and a request whose first token of the step has position 0 starts
+// from zeros whatever its slot holds.  A step's
 // tokens lie request after request: request r owns rows q_start[r] .. q_start[r + 1] - 1.
 // T is the element type of the projections' results; everything inside is float32.
 #include "common.cuh"
@@ -55,7 +56,7 @@ __global__ void conv_state_kernel(float* __restrict__ state, const T* __restrict
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   const int lo = q_start[r], n = q_start[r + 1] - lo;
-  if (n <= 0) return;
+  if (n <= 0 || state_slot[r] < 0) return;
   const int pos0 = positions[lo];
   float* st = state + (size_t)state_slot[r] * (taps - 1) * channels;
   for (int j = 0; j < taps - 1; ++j) {
@@ -82,7 +83,7 @@ selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float
   pdl_launch_dependents();
   const int r = blockIdx.y;
   const int lo = q_start[r], hi = q_start[r + 1];
-  if (hi <= lo) return;
+  if (hi <= lo || state_slot[r] < 0) return;
   const int sub = threadIdx.x & 7;
   const int c_raw = blockIdx.x * 16 + (threadIdx.x >> 3);
   const bool live = c_raw < inner;
@@ -145,7 +146,7 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
   pdl_launch_dependents();
   const int r = blockIdx.z, h = blockIdx.y;
   const int lo = q_start[r], hi = q_start[r + 1];
-  if (hi <= lo) return;
+  if (hi <= lo || state_slot[r] < 0) return;
   const int sub = threadIdx.x & 7;
   const int j_raw = blockIdx.x * 16 + (threadIdx.x >> 3);
   const bool live = j_raw < dv;

@@ -352,7 +352,7 @@ class Engine:
         put("tok_req", np.repeat(np.arange(R, dtype=np.int32), b.q_lens), fill=-1)
         put("q_start", np.concatenate([[0], np.cumsum(b.q_lens)]).astype(np.int32), fill=T)
         put("ctx_len", [s + n for s, n in zip(b.starts, b.q_lens)])
-        put("state_slot", b.state_slots)
+        put("state_slot", b.state_slots, fill=-1)
         put("fresh", b.fresh)
         lo, n = layout.seg["logit_rows"]
         if layout.static_rows:
@@ -427,10 +427,11 @@ class Engine:
         """What names the captured graph that can run this step, or 0: the padded batch size for a
         step of single tokens (lite_llama captures its decode step for batch sizes 1, 2, 4, 8, 16,
         ...: lite_llama/executor/cuda_graph.py:6-7,113-132), a padded shape (a tuple) for a step that
-        holds prompt portions.  Only for models whose mixers keep nothing but paged keys and values."""
+        holds prompt portions.  Per-request states that mixers name are fine (their kernels skip rows
+        whose state slot is negative, as every row is while a step is captured); a model without pages is not captured."""
         if not self.config.compiled_model or self.device.type != "cuda" or self.config.timing:
             return 0          # (timing brackets every operator with events, which a capture cannot hold)
-        if any(not grp.paged or grp.state or grp.states for grp in self.cache.groups):
+        if any(grp.state for grp in self.cache.groups) or not any(grp.paged for grp in self.cache.groups):
             return 0
         if batch.max_q_len != 1:
             return self._shape_bucket(batch) if self.config.capture_mixed_steps else 0
@@ -543,7 +544,7 @@ class Engine:
         host = torch.empty(layout.size, dtype=torch.int32, pin_memory=True)
         h = host.numpy()
         h.fill(0)
-        for name, fill in [("tok_req", -1), ("token_src", -1)] + [(f"slots{g}", -1) for g in layout.groups] + [(f"bt{g}", -1) for g in layout.groups]:
+        for name, fill in [("tok_req", -1), ("token_src", -1), ("state_slot", -1)] + [(f"slots{g}", -1) for g in layout.groups] + [(f"bt{g}", -1) for g in layout.groups]:
             lo, n = layout.seg[name]
             h[lo:lo + n] = fill
         if layout.static_rows:

@@ -276,6 +276,23 @@ def test_every_cut_gives_the_whole_sequence_logits(folders, dtype, name, page):
         assert eng.cache.free_slots() == 4 and all(eng.cache.free_pages(g) == pages for g in eng._paged_groups())
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_steps_from_captured_graphs(folders, dtype):
+    """Decode steps and repeated shapes of mixed steps run from CUDA graphs; the per-request states pass through them
+    (rows of a padded shape have no state slot and are skipped)."""
+    folder = folders("P", dtype)
+    seqs = {f"g{i}": random_tokens(n, 96, 300 + i) for i, n in enumerate([40, 7, 55, 21, 33])}
+    ref = _reference(folder, seqs)
+    eng = _engine(folder, dtype, 4, 80, compiled_model=True)
+    for turn in range(3):           # the same steps again: shapes seen twice are captured, then replayed
+        for family in (traces.prefill_then_decode, traces.mixed):
+            got = traces.replay(eng, family(seqs))
+            for r in seqs:
+                _assert_logits(got[r], ref[r], dtype, f"turn {turn} {family.__name__} {r}")
+    assert any(isinstance(k, tuple) for k in eng._graphs) and any(not isinstance(k, tuple) for k in eng._graphs)
+    eng.check_device_status()
+
+
 @pytest.mark.parametrize("seed", [1, 2])
 def test_random_traces_in_float32(folders, seed):
     folder = folders("Q", "float32")

@@ -146,6 +146,19 @@ def test_each_mechanism_alone(folders, kind):
             assert (got[r].double() - ref[r]).abs().max() < TOL, (kind, family.__name__, r)
 
 
+def test_a_model_without_pages(folders):
+    """Only selective-scan layers: no keys and values at all, states alone."""
+    cfg = plain.config(50, 32, 2, [plain.layer("mamba1", plain.scan(24, 4, 2, 3), plain.dense(40, 2.0)),
+                                   plain.layer("mamba1", plain.scan(40, 9, 5, 4), None)], scale=1.5)
+    folder = folders("scans", cfg, seed=9)
+    seqs = {"a": random_tokens(37, 50, 1), "b": random_tokens(8, 50, 2), "c": random_tokens(21, 50, 3)}
+    ref = _reference(folder, seqs)
+    for family in (traces.whole, traces.portions, traces.mixed):
+        got = traces.replay(_engine(folder, 4, 8, slots=2), family(seqs, live=2) if family is traces.mixed else family(seqs))
+        for r in seqs:
+            assert (got[r].double() - ref[r]).abs().max() < TOL, (family.__name__, r)
+
+
 def test_batches_of_unequal_requests_against_each_alone(folders):
     folder = folders("P")
     seqs = {"long": random_tokens(61, 96, 7), "short": random_tokens(3, 96, 8), "one": random_tokens(1, 96, 9)}
