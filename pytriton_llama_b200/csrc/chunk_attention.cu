@@ -57,7 +57,7 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
                        const float* __restrict__ q_bias, const T* __restrict__ cache, const int* __restrict__ block_table,
                        int table_width, const int* __restrict__ tok_req, const int* __restrict__ positions, int H, int G, int d,
                        int dv, int page_size, float scale, int chunk, const float* __restrict__ r1, const float* __restrict__ r2,
-                       const float* __restrict__ talk, int max_keys, int num_pages, float out_scale) {
+                       const float* __restrict__ talk, int max_keys, int num_pages, float out_scale, int vec_ok) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   long long* page_at = reinterpret_cast<long long*>(smem_raw);       // first element of the page that holds key j, -1: none
   float* q = reinterpret_cast<float*>(page_at + max_keys);
@@ -90,7 +90,16 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
       const T* kr = cache + page_at[j] + ((size_t)(h / group) * page_size + (lo + j) % page_size) * d;
       const float* qh = q + h * d;
       float acc = 0.f;
-      for (int e = 0; e < d; ++e) acc = fmaf(qh[e], to_f32(kr[e]), acc);
+      if (vec_ok) {                                     // 16-byte packets of the key row
+        constexpr int VN = Vec16<T>::N;
+        for (int e = 0; e < d; e += VN) {
+          const Vec16<T> kv = load16(kr + e);
+#pragma unroll
+          for (int u = 0; u < VN; ++u) acc = fmaf(qh[e + u], kv.get(u), acc);
+        }
+      } else {
+        for (int e = 0; e < d; ++e) acc = fmaf(qh[e], to_f32(kr[e]), acc);
+      }
       s = acc * scale;
       if (r1) s -= r1[h] * log1pf(r2[h] * (float)(p - lo - j));
     }
@@ -164,9 +173,10 @@ int chunk_attention(void* out, int out_ld, int column, const void* qkv, int q_ld
   static SmemRaised raised = {};
   if (smem > 48 * 1024)
     if (int rc = raise_shared_memory("chunk_attention", chunk_attention_kernel<T>, 200 * 1024, raised)) return rc;
+  const int vec_ok = d % Vec16<T>::N == 0 && dv % Vec16<T>::N == 0 && aligned16(cache);   // every key row starts on a 16-byte boundary
   return launch_kernel("chunk_attention", chunk_attention_kernel<T>, dim3(tokens), dim3(256), smem, as_stream(stream), (T*)out,
                        out_ld, column, (const T*)qkv, q_ld, q_bias, (const T*)cache, block_table, table_width, tok_req, positions,
-                       H, G, d, dv, page_size, scale, chunk, r1, r2, talk, max_keys, num_pages, out_scale);
+                       H, G, d, dv, page_size, scale, chunk, r1, r2, talk, max_keys, num_pages, out_scale, vec_ok);
 }
 
 }  // namespace ptl

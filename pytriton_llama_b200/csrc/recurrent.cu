@@ -72,22 +72,32 @@ __global__ void conv_state_kernel(float* __restrict__ state, const T* __restrict
 // Per channel c and state n:  S <- exp(dt A[c, n]) S + dt x B_n;  y = sum_n S C_n + D x;  out = y * silu(z),
 // dt = softplus(dt_raw[t, c] + dt_bias[c]).  Eight lanes share a channel, lane l holding states l, l + 8, ...
 // (NPL of them); a block of 128 threads walks 16 channels of one request through its tokens in order.
+// The tokens come in batches of `tb`: the block first brings a batch's B | C rows, its 16 channels' x, step sizes
+// (softplus applied) and gates (silu applied) into shared memory with all threads, so that the walk, whose steps
+// depend on one another, waits for shared memory only; the batch's results leave the same way.
+// Shared memory: tb * (2 * n_state + 64) floats.
 template <typename T, int NPL>
 __global__ void __launch_bounds__(128)
 selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float* __restrict__ dt_raw,
                       const float* __restrict__ dt_bias, const float* __restrict__ A, const T* __restrict__ bc,
                       const float* __restrict__ D, const T* __restrict__ z, int z_ld, int z_column, int inner, int n_state,
                       float* __restrict__ state, const int* __restrict__ q_start, const int* __restrict__ positions,
-                      const int* __restrict__ state_slot) {
+                      const int* __restrict__ state_slot, int tb) {
+  extern __shared__ __align__(16) float scan_smem[];
+  float* s_bc = scan_smem;                        // [tb][2 * n_state]
+  float* s_x = s_bc + (size_t)tb * 2 * n_state;   // [tb][16]
+  float* s_dt = s_x + tb * 16;
+  float* s_gate = s_dt + tb * 16;
+  float* s_y = s_gate + tb * 16;
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.y;
   const int lo = q_start[r], hi = q_start[r + 1];
   if (hi <= lo || state_slot[r] < 0) return;
-  const int sub = threadIdx.x & 7;
-  const int c_raw = blockIdx.x * 16 + (threadIdx.x >> 3);
-  const bool live = c_raw < inner;
-  const int c = live ? c_raw : inner - 1;             // lanes past the end shadow the last channel and store nothing
+  const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
+  const int c0 = blockIdx.x * 16;
+  const bool live = c0 + grp < inner;
+  const int c = live ? c0 + grp : inner - 1;          // lanes past the end shadow the last channel and store nothing
   float* st = state + ((size_t)state_slot[r] * inner + c) * n_state;
   const bool from_zero = positions[lo] == 0;
   float S[NPL], a[NPL];
@@ -97,27 +107,41 @@ selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float
     S[i] = (n < n_state && !from_zero) ? st[n] : 0.f;
     a[i] = n < n_state ? A[(size_t)c * n_state + n] : 0.f;
   }
-  const float bias = dt_bias[c], skip = D[c];
-  for (int t = lo; t < hi; ++t) {
-    const float x = to_f32(xc[(size_t)t * inner + c]);
-    const float dt = softplus_f32(dt_raw[(size_t)t * inner + c] + bias);
-    const T* bcr = bc + (size_t)t * 2 * n_state;
-    const float dx = dt * x;
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < NPL; ++i) {
-      const int n = sub + 8 * i;
-      if (n < n_state) {
-        S[i] = fmaf(expf(dt * a[i]), S[i], dx * to_f32(bcr[n]));
-        acc = fmaf(S[i], to_f32(bcr[n_state + n]), acc);
-      }
+  const float skip = D[c];
+  for (int t0 = lo; t0 < hi; t0 += tb) {
+    const int nb = min(tb, hi - t0);
+    __syncthreads();                                  // the batch before has been walked and written out
+    for (int i = threadIdx.x; i < nb * 2 * n_state; i += blockDim.x) s_bc[i] = to_f32(bc[(size_t)t0 * 2 * n_state + i]);
+    for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) {
+      const int tok = i >> 4, ch = min(c0 + (i & 15), inner - 1);
+      const size_t row = (size_t)(t0 + tok);
+      s_x[i] = to_f32(xc[row * inner + ch]);
+      s_dt[i] = softplus_f32(dt_raw[row * inner + ch] + dt_bias[ch]);
+      s_gate[i] = silu_f32(to_f32(z[row * z_ld + z_column + ch]));
     }
-    acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-    acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-    if (sub == 0 && live) {
-      const float g = to_f32(z[(size_t)t * z_ld + z_column + c]);
-      out[(size_t)t * inner + c] = from_f32<T>((acc + skip * x) * silu_f32(g));
+    __syncthreads();
+    for (int tok = 0; tok < nb; ++tok) {
+      const float x = s_x[tok * 16 + grp], dt = s_dt[tok * 16 + grp];
+      const float* brow = s_bc + (size_t)tok * 2 * n_state;
+      const float dx = dt * x;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < NPL; ++i) {
+        const int n = sub + 8 * i;
+        if (n < n_state) {
+          S[i] = fmaf(expf(dt * a[i]), S[i], dx * brow[n]);
+          acc = fmaf(S[i], brow[n_state + n], acc);
+        }
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (sub == 0) s_y[tok * 16 + grp] = (acc + skip * x) * s_gate[tok * 16 + grp];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) {
+      const int tok = i >> 4, ch = c0 + (i & 15);
+      if (ch < inner) out[(size_t)(t0 + tok) * inner + ch] = from_f32<T>(s_y[i]);
     }
   }
   if (live) {
@@ -135,22 +159,34 @@ selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float
 //     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
 // A column S[:, j] is independent of the others: eight lanes share a column, lane l holding rows l, l + 8, ...
 // (RPL of them); a block of 128 threads walks 16 columns of one head of one request through its tokens.
+// The tokens come in batches of kDeltaBatch: all threads bring the batch's q and k of the head (once, not once per
+// column), its 16 values, gates and decays into shared memory and scale q and k, then the walk reads shared memory only.
 // qkv rows: [q: kv_heads * d | k: kv_heads * d | v: heads * dv];  ba rows: [b: heads | a: heads] float32.
+// Shared memory: kDeltaBatch * (2 * d + 16 + 2) floats.
+constexpr int kDeltaBatch = 16;
+
 template <typename T, int RPL>
 __global__ void __launch_bounds__(128)
 gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, const float* __restrict__ ba,
                         const float* __restrict__ rate, const float* __restrict__ dt_bias, float* __restrict__ state,
                         const int* __restrict__ q_start, const int* __restrict__ positions, const int* __restrict__ state_slot,
                         int heads, int kv_heads, int d, int dv, float unit_eps, float q_scale) {
+  extern __shared__ __align__(16) float delta_smem[];
+  float* s_q = delta_smem;                         // [batch][d], scaled
+  float* s_k = s_q + kDeltaBatch * d;
+  float* s_v = s_k + kDeltaBatch * d;              // [batch][16]
+  float* s_beta = s_v + kDeltaBatch * 16;
+  float* s_g = s_beta + kDeltaBatch;
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.z, h = blockIdx.y;
   const int lo = q_start[r], hi = q_start[r + 1];
   if (hi <= lo || state_slot[r] < 0) return;
-  const int sub = threadIdx.x & 7;
-  const int j_raw = blockIdx.x * 16 + (threadIdx.x >> 3);
-  const bool live = j_raw < dv;
-  const int j = live ? j_raw : dv - 1;
+  const int sub = threadIdx.x & 7, grp = threadIdx.x >> 3;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int j0 = blockIdx.x * 16;
+  const bool live = j0 + grp < dv;
+  const int j = live ? j0 + grp : dv - 1;
   const int c = h / (heads / kv_heads);
   const int ld = 2 * kv_heads * d + heads * dv;
   float* st = state + (((size_t)state_slot[r] * heads + h) * d) * dv + j;
@@ -162,47 +198,58 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
     S[i] = (row < d && !from_zero) ? st[(size_t)row * dv] : 0.f;
   }
   const float rate_h = rate[h], bias_h = dt_bias[h];
-  for (int t = lo; t < hi; ++t) {
-    const T* row = qkv + (size_t)t * ld;
-    float q[RPL], k[RPL];
-    float qq = 0.f, kk = 0.f;
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      const int e = sub + 8 * i;
-      q[i] = e < d ? to_f32(row[c * d + e]) : 0.f;
-      k[i] = e < d ? to_f32(row[(kv_heads + c) * d + e]) : 0.f;
-      qq = fmaf(q[i], q[i], qq);
-      kk = fmaf(k[i], k[i], kk);
+  for (int t0 = lo; t0 < hi; t0 += kDeltaBatch) {
+    const int nb = min(kDeltaBatch, hi - t0);
+    __syncthreads();                                  // the batch before has been walked
+    for (int tok = warp; tok < nb; tok += 4) {        // a warp per token: fetch q and k, then scale them to unit length
+      const T* row = qkv + (size_t)(t0 + tok) * ld;
+      float qq = 0.f, kk = 0.f;
+      for (int e = lane; e < d; e += 32) {
+        const float qv = to_f32(row[c * d + e]), kv = to_f32(row[(kv_heads + c) * d + e]);
+        s_q[tok * d + e] = qv;
+        s_k[tok * d + e] = kv;
+        qq = fmaf(qv, qv, qq);
+        kk = fmaf(kv, kv, kk);
+      }
+      qq = warp_sum(qq);
+      kk = warp_sum(kk);
+      const float qn = q_scale / sqrtf(qq + unit_eps), kn = 1.0f / sqrtf(kk + unit_eps);
+      for (int e = lane; e < d; e += 32) {            // (each lane scales what it wrote itself)
+        s_q[tok * d + e] *= qn;
+        s_k[tok * d + e] *= kn;
+      }
+      if (lane < 16) s_v[tok * 16 + lane] = to_f32(row[2 * kv_heads * d + h * dv + min(j0 + lane, dv - 1)]);
+      if (lane == 16) s_beta[tok] = 1.0f / (1.0f + expf(-ba[(size_t)(t0 + tok) * 2 * heads + h]));
+      if (lane == 17) s_g[tok] = expf(-rate_h * softplus_f32(ba[(size_t)(t0 + tok) * 2 * heads + heads + h] + bias_h));
     }
+    __syncthreads();
+    for (int tok = 0; tok < nb; ++tok) {
+      const float* kp = s_k + tok * d;
+      const float* qp = s_q + tok * d;
+      const float g = s_g[tok];
+      float k[RPL];
+      float dot = 0.f;
 #pragma unroll
-    for (int o = 1; o < 8; o <<= 1) {
-      qq += __shfl_xor_sync(0xffffffffu, qq, o);
-      kk += __shfl_xor_sync(0xffffffffu, kk, o);
+      for (int i = 0; i < RPL; ++i) {
+        const int e = sub + 8 * i;
+        k[i] = e < d ? kp[e] : 0.f;
+        S[i] *= g;
+        dot = fmaf(S[i], k[i], dot);
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
+      const float u = s_beta[tok] * (s_v[tok * 16 + grp] - dot);
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPL; ++i) {
+        const int e = sub + 8 * i;
+        S[i] = fmaf(k[i], u, S[i]);
+        acc = fmaf(S[i], e < d ? qp[e] : 0.f, acc);
+      }
+#pragma unroll
+      for (int o = 1; o < 8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (sub == 0 && live) out[(size_t)(t0 + tok) * heads * dv + h * dv + j] = acc;
     }
-    const float qn = q_scale / sqrtf(qq + unit_eps), kn = 1.0f / sqrtf(kk + unit_eps);
-    const float v = to_f32(row[2 * kv_heads * d + h * dv + j]);
-    const float beta = 1.0f / (1.0f + expf(-ba[(size_t)t * 2 * heads + h]));
-    const float g = expf(-rate_h * softplus_f32(ba[(size_t)t * 2 * heads + heads + h] + bias_h));
-    float dot = 0.f;
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      k[i] *= kn;
-      q[i] *= qn;
-      S[i] *= g;
-      dot = fmaf(S[i], k[i], dot);
-    }
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-    const float u = beta * (v - dot);
-    float acc = 0.f;
-#pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      S[i] = fmaf(k[i], u, S[i]);
-      acc = fmaf(S[i], q[i], acc);
-    }
-#pragma unroll
-    for (int o = 1; o < 8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-    if (sub == 0 && live) out[(size_t)t * heads * dv + h * dv + j] = acc;
   }
   if (live) {
 #pragma unroll
@@ -266,9 +313,11 @@ int selective_scan(void* out, const void* xc, const float* dt_raw, const float* 
   PTL_REQUIRE(requests <= 65535, "selective_scan: at most 65535 requests per step, got %d", requests);
   if (requests == 0) return 0;
   const dim3 grid((inner + 15) / 16, requests), block(128);
-#define PTL_SCAN(NPL) return launch_kernel("selective_scan", selective_scan_kernel<T, NPL>, grid, block, 0, as_stream(stream), \
+  const int tb = n_state <= 64 ? 32 : (n_state <= 128 ? 16 : 8);          // at most 20 KB of shared memory
+  const size_t smem = (size_t)tb * (2 * n_state + 64) * sizeof(float);
+#define PTL_SCAN(NPL) return launch_kernel("selective_scan", selective_scan_kernel<T, NPL>, grid, block, smem, as_stream(stream), \
     (T*)out, (const T*)xc, dt_raw, dt_bias, A, (const T*)bc, D, (const T*)z, z_ld, z_column, inner, n_state, state, q_start, \
-    positions, state_slot)
+    positions, state_slot, tb)
   const int per_lane = (n_state + 7) / 8;
   if (per_lane <= 1) PTL_SCAN(1);
   if (per_lane <= 2) PTL_SCAN(2);
@@ -289,7 +338,8 @@ int gated_delta_rule(float* out, const void* qkv, const float* ba, const float* 
   PTL_REQUIRE(requests <= 65535 && heads <= 65535, "gated_delta_rule: at most 65535 requests and heads");
   if (requests == 0) return 0;
   const dim3 grid((dv + 15) / 16, heads, requests), block(128);
-#define PTL_DELTA(RPL) return launch_kernel("gated_delta_rule", gated_delta_rule_kernel<T, RPL>, grid, block, 0, as_stream(stream), \
+  const size_t smem = (size_t)kDeltaBatch * (2 * d + 16 + 2) * sizeof(float);     // at most 34 KB
+#define PTL_DELTA(RPL) return launch_kernel("gated_delta_rule", gated_delta_rule_kernel<T, RPL>, grid, block, smem, as_stream(stream), \
     out, (const T*)qkv, ba, rate, dt_bias, state, q_start, positions, state_slot, heads, kv_heads, d, dv, unit_eps, q_scale)
   const int per_lane = (d + 7) / 8;
   if (per_lane <= 2) PTL_DELTA(2);

@@ -63,52 +63,115 @@ __device__ __forceinline__ float gelu_tanh(float z) {
   return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
-// One block per token.  s = residual + x + bias;  z = W_gate s;  g = gelu_tanh(z) * table[token, column + j];
-// y = W_proj g;  residual = s + y * rsqrt(mean(y^2) + eps) * norm.   Shared memory: 2 * width + 2 * dim floats.
-template <typename T>
+// A block takes TPB consecutive tokens.  s = residual + x + bias;  z = W_gate s;  g = gelu_tanh(z) * table[token, column + j];
+// y = W_proj g;  residual = s + y * rsqrt(mean(y^2) + eps) * norm.   Every weight row is fetched once per block (16-byte
+// packets where `vec_ok`) and used for all of the block's tokens.  Shared memory: TPB * (2 * width + dim) floats.
+template <typename T, int TPB>
 __global__ void __launch_bounds__(256)
 token_side_kernel(float* __restrict__ residual, const T* __restrict__ x, const float* __restrict__ bias,
                   const int* __restrict__ tokens, const T* __restrict__ table, int table_ld, int column, int dim, int vocab,
                   const T* __restrict__ w_gate, const T* __restrict__ w_proj, const float* __restrict__ norm_w, int width,
-                  float eps) {
-  extern __shared__ float smem[];
+                  float eps, int n_tokens, int vec_ok) {
+  extern __shared__ __align__(16) float smem[];
   __shared__ float red[33];
   float* s = smem;
-  float* y = smem + width;
-  float* g = y + width;
+  float* y = s + (size_t)TPB * width;
+  float* g = y + (size_t)TPB * width;
+  constexpr int VN = Vec16<T>::N;
   pdl_wait();
   pdl_launch_dependents();
-  const int t = blockIdx.x;
+  const int t0 = blockIdx.x * TPB;
+  const int nt = min(TPB, n_tokens - t0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  float* res = residual + (size_t)t * width;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    float v = res[i];
-    if (x) v += to_f32(x[(size_t)t * width + i]);
-    if (bias) v += bias[i];
-    s[i] = v;
+  for (int k = 0; k < TPB; ++k) {
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float v = 0.f;
+      if (k < nt) {
+        v = residual[(size_t)(t0 + k) * width + i];
+        if (x) v += to_f32(x[(size_t)(t0 + k) * width + i]);
+        if (bias) v += bias[i];
+      }
+      s[(size_t)k * width + i] = v;
+    }
   }
   __syncthreads();
-  int tok = tokens[t];
-  if (tok < 0 || tok >= vocab) tok = 0;
   for (int j = warp; j < dim; j += nwarps) {
     const T* wr = w_gate + (size_t)j * width;
-    float acc = 0.f;
-    for (int i = lane; i < width; i += 32) acc = fmaf(s[i], to_f32(wr[i]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) g[j] = gelu_tanh(acc) * to_f32(table[(size_t)tok * table_ld + column + j]);
+    float acc[TPB];
+#pragma unroll
+    for (int k = 0; k < TPB; ++k) acc[k] = 0.f;
+    if (vec_ok) {
+      for (int i = lane * VN; i < width; i += 32 * VN) {
+        const Vec16<T> v = load16(wr + i);
+#pragma unroll
+        for (int k = 0; k < TPB; ++k) {
+#pragma unroll
+          for (int e = 0; e < VN; e += 4) {      // (16-byte reads of the row in shared memory: width is a multiple of VN here)
+            const float4 a = *reinterpret_cast<const float4*>(s + (size_t)k * width + i + e);
+            acc[k] = fmaf(a.x, v.get(e), acc[k]);
+            acc[k] = fmaf(a.y, v.get(e + 1), acc[k]);
+            acc[k] = fmaf(a.z, v.get(e + 2), acc[k]);
+            acc[k] = fmaf(a.w, v.get(e + 3), acc[k]);
+          }
+        }
+      }
+    } else {
+      for (int i = lane; i < width; i += 32) {
+        const float wv = to_f32(wr[i]);
+#pragma unroll
+        for (int k = 0; k < TPB; ++k) acc[k] = fmaf(s[(size_t)k * width + i], wv, acc[k]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < TPB; ++k) {
+      const float z = warp_sum(acc[k]);
+      if (lane == 0) {
+        int tok = k < nt ? tokens[t0 + k] : 0;
+        if (tok < 0 || tok >= vocab) tok = 0;
+        g[k * dim + j] = gelu_tanh(z) * to_f32(table[(size_t)tok * table_ld + column + j]);
+      }
+    }
   }
   __syncthreads();
-  float ss = 0.f;
+  float ss[TPB];
+#pragma unroll
+  for (int k = 0; k < TPB; ++k) ss[k] = 0.f;
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const T* wr = w_proj + (size_t)i * dim;
-    float acc = 0.f;
-    for (int j = 0; j < dim; ++j) acc = fmaf(g[j], to_f32(wr[j]), acc);
-    y[i] = acc;
-    ss += acc * acc;
+    float acc[TPB];
+#pragma unroll
+    for (int k = 0; k < TPB; ++k) acc[k] = 0.f;
+    if (vec_ok) {
+      for (int j = 0; j < dim; j += VN) {
+        const Vec16<T> v = load16(wr + j);
+#pragma unroll
+        for (int e = 0; e < VN; ++e) {
+          const float wv = v.get(e);
+#pragma unroll
+          for (int k = 0; k < TPB; ++k) acc[k] = fmaf(g[k * dim + j + e], wv, acc[k]);
+        }
+      }
+    } else {
+      for (int j = 0; j < dim; ++j) {
+        const float wv = to_f32(wr[j]);
+#pragma unroll
+        for (int k = 0; k < TPB; ++k) acc[k] = fmaf(g[k * dim + j], wv, acc[k]);
+      }
+    }
+#pragma unroll
+    for (int k = 0; k < TPB; ++k) {
+      y[(size_t)k * width + i] = acc[k];
+      ss[k] = fmaf(acc[k], acc[k], ss[k]);
+    }
   }
-  ss = block_sum(ss, red);
-  const float rrms = 1.0f / sqrtf(ss / (float)width + eps);
-  for (int i = threadIdx.x; i < width; i += blockDim.x) res[i] = s[i] + y[i] * rrms * norm_w[i];
+#pragma unroll
+  for (int k = 0; k < TPB; ++k) {
+    const float total = block_sum(ss[k], red);
+    if (k >= nt) continue;
+    const float rrms = 1.0f / sqrtf(total / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+      residual[(size_t)(t0 + k) * width + i] = s[(size_t)k * width + i] + y[(size_t)k * width + i] * rrms * norm_w[i];
+  }
 }
 
 template <typename T>
@@ -130,6 +193,19 @@ int clamped_glu(void* out, const void* gu, const float* bias, int tokens, int in
                        (T*)out, (const T*)gu, bias, inter, limit, alpha, up_shift);
 }
 
+template <typename T, int TPB>
+int token_side_launch(float* residual, const void* x, const float* bias, const int* tokens, const void* table, int table_ld,
+                      int column, int dim, int vocab, const void* w_gate, const void* w_proj, const float* norm_w, int n_tokens,
+                      int width, float eps, int vec_ok, void* stream) {
+  const size_t smem = (size_t)TPB * (2 * width + dim) * sizeof(float);
+  static SmemRaised raised = {};
+  if (smem > 48 * 1024)
+    if (int rc = raise_shared_memory("token_side", token_side_kernel<T, TPB>, 200 * 1024, raised)) return rc;
+  return launch_kernel("token_side", token_side_kernel<T, TPB>, dim3((n_tokens + TPB - 1) / TPB), dim3(256), smem,
+                       as_stream(stream), residual, (const T*)x, bias, tokens, (const T*)table, table_ld, column, dim, vocab,
+                       (const T*)w_gate, (const T*)w_proj, norm_w, width, eps, n_tokens, vec_ok);
+}
+
 template <typename T>
 int token_side(float* residual, const void* x, const float* bias, const int* tokens, const void* table, int table_ld, int column,
                int dim, int vocab, const void* w_gate, const void* w_proj, const float* norm_w, int n_tokens, int width, float eps,
@@ -137,14 +213,16 @@ int token_side(float* residual, const void* x, const float* bias, const int* tok
   PTL_REQUIRE(n_tokens >= 0 && width > 0 && dim > 0 && column >= 0 && column + dim <= table_ld && eps > 0.f,
               "token_side: bad sizes tokens=%d width=%d dim=%d column=%d of %d", n_tokens, width, dim, column, table_ld);
   if (n_tokens == 0) return 0;
-  const size_t smem = (size_t)(2 * width + dim) * sizeof(float);
-  PTL_REQUIRE(smem <= 200 * 1024, "token_side: width=%d, dim=%d do not fit the shared memory of a block", width, dim);
-  static SmemRaised raised = {};
-  if (smem > 48 * 1024)
-    if (int rc = raise_shared_memory("token_side", token_side_kernel<T>, 200 * 1024, raised)) return rc;
-  return launch_kernel("token_side", token_side_kernel<T>, dim3(n_tokens), dim3(256), smem, as_stream(stream), residual,
-                       (const T*)x, bias, tokens, (const T*)table, table_ld, column, dim, vocab, (const T*)w_gate,
-                       (const T*)w_proj, norm_w, width, eps);
+  const size_t per_token = (size_t)(2 * width + dim) * sizeof(float);
+  PTL_REQUIRE(per_token <= 200 * 1024, "token_side: width=%d, dim=%d do not fit the shared memory of a block", width, dim);
+  constexpr int VN = Vec16<T>::N;
+  const int vec_ok = width % VN == 0 && dim % VN == 0 && aligned16(w_gate) && aligned16(w_proj);
+  // many tokens: four per block, so that a block's pass over the two weights serves four rows
+  if (n_tokens >= 64 && 4 * per_token <= 200 * 1024)
+    return token_side_launch<T, 4>(residual, x, bias, tokens, table, table_ld, column, dim, vocab, w_gate, w_proj, norm_w, n_tokens,
+                                   width, eps, vec_ok, stream);
+  return token_side_launch<T, 1>(residual, x, bias, tokens, table, table_ld, column, dim, vocab, w_gate, w_proj, norm_w, n_tokens,
+                                 width, eps, vec_ok, stream);
 }
 
 }  // namespace ptl

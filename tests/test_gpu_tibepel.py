@@ -289,8 +289,21 @@ def test_steps_from_captured_graphs(folders, dtype):
             got = traces.replay(eng, family(seqs))
             for r in seqs:
                 _assert_logits(got[r], ref[r], dtype, f"turn {turn} {family.__name__} {r}")
-    assert any(isinstance(k, tuple) for k in eng._graphs) and any(not isinstance(k, tuple) for k in eng._graphs)
+    assert any(not isinstance(k, tuple) for k in eng._graphs)             # decode steps were captured
     eng.check_device_status()
+    # steps with prompt portions that want one row at most are captured when their shape comes again: generation
+    from pytriton_llama_b200 import LLM, EngineConfig, SamplingParams
+    prompts = [random_tokens(n, 96, 60 + i) for i, n in enumerate([30, 9, 41, 17, 26, 35])]
+    outs = {}
+    for graphs in (False, True):
+        cfg = EngineConfig(dtype=dtype, page_size=4, max_gpu_num_blocks=96, max_seq_len=96, max_num_seqs=3, max_batched_tokens=24,
+                           compiled_model=graphs)
+        llm = LLM(folder, cfg)
+        outs[graphs] = [llm.generate(prompts, SamplingParams(temperature=0.0, max_gen_len=10)) for _ in range(3)]
+        if graphs:
+            assert any(isinstance(k, tuple) for k in llm.engine._graphs)
+    if dtype == "float32":
+        assert outs[True] == outs[False] and outs[True][0] == outs[True][2]
 
 
 @pytest.mark.parametrize("seed", [1, 2])
