@@ -120,7 +120,8 @@ selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float
       s_gate[i] = silu_f32(to_f32(z[row * z_ld + z_column + ch]));
     }
     __syncthreads();
-    for (int tok = 0; tok < nb; ++tok) {
+#pragma unroll 4
+    for (int tok = 0; tok < nb; ++tok) {      // (four tokens per turn: only S links them, the sums over lanes overlap)
       const float x = s_x[tok * 16 + grp], dt = s_dt[tok * 16 + grp];
       const float* brow = s_bc + (size_t)tok * 2 * n_state;
       const float dx = dt * x;
@@ -159,10 +160,13 @@ selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float
 //     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
 // A column S[:, j] is independent of the others: eight lanes share a column, lane l holding rows l, l + 8, ...
 // (RPL of them); a block of 128 threads walks 16 columns of one head of one request through its tokens.
-// The tokens come in batches of kDeltaBatch: all threads bring the batch's q and k of the head (once, not once per
-// column), its 16 values, gates and decays into shared memory and scale q and k, then the walk reads shared memory only.
+// The tokens come in batches of kDeltaBatch.  All threads bring a batch's q and k of the head (once, not once per
+// column), its 16 values, gates and decays into shared memory, and hold the next batch's q and k in registers while the
+// current one is walked, so that the walk, whose steps depend on one another, never waits for global memory.  The unit
+// scaling is folded into the walk: with kn = 1 / |k| and qn = q_scale / |q|,
+//     dot = kn * (S^T k);  u = beta (v - dot);  S <- S + k (kn u);  o = qn * (S^T q).
 // qkv rows: [q: kv_heads * d | k: kv_heads * d | v: heads * dv];  ba rows: [b: heads | a: heads] float32.
-// Shared memory: kDeltaBatch * (2 * d + 16 + 2) floats.
+// Shared memory: kDeltaBatch * (2 * d + 16 + 4) floats.
 constexpr int kDeltaBatch = 16;
 
 template <typename T, int RPL>
@@ -172,11 +176,13 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
                         const int* __restrict__ q_start, const int* __restrict__ positions, const int* __restrict__ state_slot,
                         int heads, int kv_heads, int d, int dv, float unit_eps, float q_scale) {
   extern __shared__ __align__(16) float delta_smem[];
-  float* s_q = delta_smem;                         // [batch][d], scaled
+  float* s_q = delta_smem;                         // [batch][d], as projected
   float* s_k = s_q + kDeltaBatch * d;
   float* s_v = s_k + kDeltaBatch * d;              // [batch][16]
   float* s_beta = s_v + kDeltaBatch * 16;
   float* s_g = s_beta + kDeltaBatch;
+  float* s_qn = s_g + kDeltaBatch;
+  float* s_kn = s_qn + kDeltaBatch;
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.z, h = blockIdx.y;
@@ -198,57 +204,89 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
     S[i] = (row < d && !from_zero) ? st[(size_t)row * dv] : 0.f;
   }
   const float rate_h = rate[h], bias_h = dt_bias[h];
+  // Element i of a thread's share of a batch: flat index threadIdx.x + 128 * i over [batch][d]; RPL of them cover
+  // kDeltaBatch * d = 16 d <= 128 * RPL (d <= 8 * RPL).  (token, element) of the flat index advance without a division.
+  float pq[RPL], pk[RPL];
+  const int tok_first = threadIdx.x / d, e_first = threadIdx.x % d, tok_step = 128 / d, e_step = 128 % d;
+  auto fetch = [&](int t0) {
+    const int nb = min(kDeltaBatch, hi - t0);
+    int tok = tok_first, e = e_first;
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      if (tok < nb) {
+        const T* row = qkv + (size_t)(t0 + tok) * ld;
+        pq[i] = to_f32(row[c * d + e]);
+        pk[i] = to_f32(row[(kv_heads + c) * d + e]);
+      }
+      tok += tok_step;
+      e += e_step;
+      if (e >= d) { e -= d; ++tok; }
+    }
+  };
+  fetch(lo);
   for (int t0 = lo; t0 < hi; t0 += kDeltaBatch) {
     const int nb = min(kDeltaBatch, hi - t0);
     __syncthreads();                                  // the batch before has been walked
-    for (int tok = warp; tok < nb; tok += 4) {        // a warp per token: fetch q and k, then scale them to unit length
-      const T* row = qkv + (size_t)(t0 + tok) * ld;
+#pragma unroll
+    for (int i = 0; i < RPL; ++i) {
+      const int idx = threadIdx.x + 128 * i;
+      if (idx < nb * d) { s_q[idx] = pq[i]; s_k[idx] = pk[i]; }
+    }
+    for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) {
+      const int tok = i >> 4;
+      s_v[i] = to_f32(qkv[(size_t)(t0 + tok) * ld + 2 * kv_heads * d + h * dv + min(j0 + (i & 15), dv - 1)]);
+    }
+    if (threadIdx.x < nb) {
+      const float* row = ba + (size_t)(t0 + threadIdx.x) * 2 * heads;
+      s_beta[threadIdx.x] = 1.0f / (1.0f + expf(-row[h]));
+      s_g[threadIdx.x] = expf(-rate_h * softplus_f32(row[heads + h] + bias_h));
+    }
+    __syncthreads();
+    if (t0 + kDeltaBatch < hi) fetch(t0 + kDeltaBatch);   // in flight while this batch is walked
+    for (int tok = warp; tok < nb; tok += 4) {           // a warp per token: the lengths of q and k
       float qq = 0.f, kk = 0.f;
       for (int e = lane; e < d; e += 32) {
-        const float qv = to_f32(row[c * d + e]), kv = to_f32(row[(kv_heads + c) * d + e]);
-        s_q[tok * d + e] = qv;
-        s_k[tok * d + e] = kv;
-        qq = fmaf(qv, qv, qq);
-        kk = fmaf(kv, kv, kk);
+        qq = fmaf(s_q[tok * d + e], s_q[tok * d + e], qq);
+        kk = fmaf(s_k[tok * d + e], s_k[tok * d + e], kk);
       }
       qq = warp_sum(qq);
       kk = warp_sum(kk);
-      const float qn = q_scale / sqrtf(qq + unit_eps), kn = 1.0f / sqrtf(kk + unit_eps);
-      for (int e = lane; e < d; e += 32) {            // (each lane scales what it wrote itself)
-        s_q[tok * d + e] *= qn;
-        s_k[tok * d + e] *= kn;
+      if (lane == 0) {
+        s_qn[tok] = q_scale / sqrtf(qq + unit_eps);
+        s_kn[tok] = 1.0f / sqrtf(kk + unit_eps);
       }
-      if (lane < 16) s_v[tok * 16 + lane] = to_f32(row[2 * kv_heads * d + h * dv + min(j0 + lane, dv - 1)]);
-      if (lane == 16) s_beta[tok] = 1.0f / (1.0f + expf(-ba[(size_t)(t0 + tok) * 2 * heads + h]));
-      if (lane == 17) s_g[tok] = expf(-rate_h * softplus_f32(ba[(size_t)(t0 + tok) * 2 * heads + heads + h] + bias_h));
     }
     __syncthreads();
-    for (int tok = 0; tok < nb; ++tok) {
+#pragma unroll (RPL <= 16 ? 2 : 1)
+    for (int tok = 0; tok < nb; ++tok) {      // (two tokens per turn: the read-out of one overlaps the update of the next)
       const float* kp = s_k + tok * d;
       const float* qp = s_q + tok * d;
-      const float g = s_g[tok];
+      const float g = s_g[tok], kn = s_kn[tok];
       float k[RPL];
-      float dot = 0.f;
+      float dot0 = 0.f, dot1 = 0.f;
 #pragma unroll
       for (int i = 0; i < RPL; ++i) {
         const int e = sub + 8 * i;
         k[i] = e < d ? kp[e] : 0.f;
         S[i] *= g;
-        dot = fmaf(S[i], k[i], dot);
+        if (i & 1) dot1 = fmaf(S[i], k[i], dot1); else dot0 = fmaf(S[i], k[i], dot0);
       }
+      float dot = dot0 + dot1;
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
-      const float u = s_beta[tok] * (s_v[tok * 16 + grp] - dot);
-      float acc = 0.f;
+      const float u = s_beta[tok] * (s_v[tok * 16 + grp] - kn * dot) * kn;
+      float acc0 = 0.f, acc1 = 0.f;
 #pragma unroll
       for (int i = 0; i < RPL; ++i) {
         const int e = sub + 8 * i;
         S[i] = fmaf(k[i], u, S[i]);
-        acc = fmaf(S[i], e < d ? qp[e] : 0.f, acc);
+        const float qv = e < d ? qp[e] : 0.f;
+        if (i & 1) acc1 = fmaf(S[i], qv, acc1); else acc0 = fmaf(S[i], qv, acc0);
       }
+      float acc = acc0 + acc1;
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (sub == 0 && live) out[(size_t)(t0 + tok) * heads * dv + h * dv + j] = acc;
+      if (sub == 0 && live) out[(size_t)(t0 + tok) * heads * dv + h * dv + j] = acc * s_qn[tok];
     }
   }
   if (live) {
@@ -338,7 +376,7 @@ int gated_delta_rule(float* out, const void* qkv, const float* ba, const float* 
   PTL_REQUIRE(requests <= 65535 && heads <= 65535, "gated_delta_rule: at most 65535 requests and heads");
   if (requests == 0) return 0;
   const dim3 grid((dv + 15) / 16, heads, requests), block(128);
-  const size_t smem = (size_t)kDeltaBatch * (2 * d + 16 + 2) * sizeof(float);     // at most 34 KB
+  const size_t smem = (size_t)kDeltaBatch * (2 * d + 16 + 4) * sizeof(float);     // at most 34 KB
 #define PTL_DELTA(RPL) return launch_kernel("gated_delta_rule", gated_delta_rule_kernel<T, RPL>, grid, block, smem, as_stream(stream), \
     out, (const T*)qkv, ba, rate, dt_bias, state, q_start, positions, state_slot, heads, kv_heads, d, dv, unit_eps, q_scale)
   const int per_lane = (d + 7) / 8;

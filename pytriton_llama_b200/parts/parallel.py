@@ -6,8 +6,16 @@ columns of one buffer, and one product with the members' output weights side by 
 (the members' output biases, scaled, are added by the caller: ``output_bias``).  At most one member
 may keep keys and values in pages; the per-request states of all members are kept under
 "<member>.<name>".
+
+On a CUDA device the members run side by side in time as well: the first on the launching stream,
+every other one on a stream of its own that starts after the input is ready and is joined before
+the output product (a member that walks its tokens in order fills few SMs for long; the others'
+kernels take the rest).  A step that is captured in a CUDA graph keeps the fork as branches of the
+graph.  ``PTL_PARALLEL_STREAMS=0`` runs the members one after another.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -30,6 +38,7 @@ class ParallelMixers(Part):
         self.inner_width = at
         self.output_bias_spec = any(getattr(m, "output_bias_spec", False) for m in self.members.values())
         self.w_o = self.output_bias = None
+        self._streams = None
 
     def children(self):
         return dict(self.members)
@@ -56,6 +65,23 @@ class ParallelMixers(Part):
     def forward(self, x, ctx, cache):
         ops = self.rt.ops
         joint = ops.empty((x.shape[0], self.inner_width), self.rt.dtype)
-        for name, m in self.members.items():
-            m.write_inner(x, ctx, cache.member(name), joint, self.columns[name], self.scales[name])
+        names = list(self.members)
+        side_by_side = (self.rt.device.type == "cuda" and len(names) > 1 and isinstance(x, torch.Tensor)
+                        and os.environ.get("PTL_PARALLEL_STREAMS", "1") != "0")
+        if not side_by_side:
+            for name in names:
+                self.members[name].write_inner(x, ctx, cache.member(name), joint, self.columns[name], self.scales[name])
+            return ops.linear(joint, self.w_o)
+        if self._streams is None:
+            self._streams = [torch.cuda.Stream(self.rt.device) for _ in names[1:]]
+        main = torch.cuda.current_stream(self.rt.device)
+        ready = torch.cuda.Event()
+        ready.record(main)
+        for name, stream in zip(names[1:], self._streams):
+            stream.wait_event(ready)
+            with torch.cuda.stream(stream):
+                self.members[name].write_inner(x, ctx, cache.member(name), joint, self.columns[name], self.scales[name])
+        self.members[names[0]].write_inner(x, ctx, cache.member(names[0]), joint, self.columns[names[0]], self.scales[names[0]])
+        for stream in self._streams:
+            main.wait_stream(stream)
         return ops.linear(joint, self.w_o)
