@@ -82,28 +82,53 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
     page_at[j] = (page >= 0 && page < num_pages) ? (long long)((size_t)page * page_stride) : -1;
   }
   __syncthreads();
-  // scores: one (head, key) pair per thread and turn; consecutive threads take consecutive keys of one head
-  for (int i = threadIdx.x; i < H * n; i += blockDim.x) {
-    const int h = i / n, j = i % n;
-    float s = -INFINITY;
-    if (page_at[j] >= 0) {
-      const T* kr = cache + page_at[j] + ((size_t)(h / group) * page_size + (lo + j) % page_size) * d;
-      const float* qh = q + h * d;
-      float acc = 0.f;
-      if (vec_ok) {                                     // 16-byte packets of the key row
+  // scores: one (kv head, key) pair per thread and turn, for up to four of the kv head's query heads at a time, so that
+  // a key row is fetched once for them; consecutive threads take consecutive keys
+  for (int i = threadIdx.x; i < G * n; i += blockDim.x) {
+    const int c = i / n, j = i % n;
+    const bool there = page_at[j] >= 0;
+    const T* kr = cache + (there ? page_at[j] : 0) + ((size_t)c * page_size + (lo + j) % page_size) * d;
+    for (int h0 = c * group; h0 < (c + 1) * group; h0 += 4) {
+      const int nh = min(4, (c + 1) * group - h0);
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (there && vec_ok) {                            // 16-byte packets of the key row and of the queries
         constexpr int VN = Vec16<T>::N;
         for (int e = 0; e < d; e += VN) {
           const Vec16<T> kv = load16(kr + e);
 #pragma unroll
-          for (int u = 0; u < VN; ++u) acc = fmaf(qh[e + u], kv.get(u), acc);
+          for (int a4 = 0; a4 < 4; ++a4) {
+            if (a4 < nh) {
+#pragma unroll
+              for (int u = 0; u < VN; u += 4) {
+                const float4 qv = *reinterpret_cast<const float4*>(q + (h0 + a4) * d + e + u);
+                acc[a4] = fmaf(qv.x, kv.get(u), acc[a4]);
+                acc[a4] = fmaf(qv.y, kv.get(u + 1), acc[a4]);
+                acc[a4] = fmaf(qv.z, kv.get(u + 2), acc[a4]);
+                acc[a4] = fmaf(qv.w, kv.get(u + 3), acc[a4]);
+              }
+            }
+          }
         }
-      } else {
-        for (int e = 0; e < d; ++e) acc = fmaf(qh[e], to_f32(kr[e]), acc);
+      } else if (there) {
+        for (int e = 0; e < d; ++e) {
+          const float kv = to_f32(kr[e]);
+#pragma unroll
+          for (int a4 = 0; a4 < 4; ++a4)
+            if (a4 < nh) acc[a4] = fmaf(q[(h0 + a4) * d + e], kv, acc[a4]);
+        }
       }
-      s = acc * scale;
-      if (r1) s -= r1[h] * log1pf(r2[h] * (float)(p - lo - j));
+#pragma unroll
+      for (int a4 = 0; a4 < 4; ++a4) {
+        if (a4 >= nh) continue;
+        const int h = h0 + a4;
+        float sc = -INFINITY;
+        if (there) {
+          sc = acc[a4] * scale;
+          if (r1) sc -= r1[h] * log1pf(r2[h] * (float)(p - lo - j));
+        }
+        w[(size_t)h * max_keys + j] = sc;
+      }
     }
-    w[(size_t)h * max_keys + j] = s;
   }
   __syncthreads();
   for (int h = warp; h < H; h += nwarps) {
@@ -133,16 +158,26 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
     __syncthreads();
     use = mixed;
   }
-  for (int i = threadIdx.x; i < H * dv; i += blockDim.x) {
-    const int h = i / dv, e = i % dv;
-    const float* wh = use + (size_t)h * max_keys;
-    const size_t head_off = (size_t)G * page_size * d + (size_t)(h / group) * page_size * dv + e;
-    float acc = 0.f;
-    for (int j = 0; j < n; ++j) {
-      if (page_at[j] < 0) continue;
-      acc = fmaf(wh[j], to_f32(cache[(size_t)page_at[j] + head_off + (size_t)((lo + j) % page_size) * dv]), acc);
+  // outputs: one (kv head, value element) pair per thread and turn, for up to four of the kv head's query heads at a
+  // time, so that a value is fetched once for them; consecutive threads take consecutive elements
+  for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
+    const int c = i / dv, e = i % dv;
+    const size_t head_off = (size_t)G * page_size * d + (size_t)c * page_size * dv + e;
+    for (int h0 = c * group; h0 < (c + 1) * group; h0 += 4) {
+      const int nh = min(4, (c + 1) * group - h0);
+      const float* w0 = use + (size_t)h0 * max_keys;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < n; ++j) {
+        if (page_at[j] < 0) continue;
+        const float v = to_f32(cache[(size_t)page_at[j] + head_off + (size_t)((lo + j) % page_size) * dv]);
+#pragma unroll
+        for (int a4 = 0; a4 < 4; ++a4)
+          if (a4 < nh) acc[a4] = fmaf(w0[(size_t)a4 * max_keys + j], v, acc[a4]);
+      }
+#pragma unroll
+      for (int a4 = 0; a4 < 4; ++a4)
+        if (a4 < nh) out[(size_t)t * out_ld + column + (h0 + a4) * dv + e] = from_f32<T>(acc[a4] * out_scale);
     }
-    out[(size_t)t * out_ld + column + i] = from_f32<T>(acc * out_scale);
   }
 }
 
@@ -167,13 +202,14 @@ int chunk_attention(void* out, int out_ld, int column, const void* qkv, int q_ld
   PTL_REQUIRE((r1 == nullptr) == (r2 == nullptr), "chunk_attention: the distance bias needs both of its factors");
   PTL_REQUIRE(column >= 0 && column + H * dv <= out_ld && q_ld >= H * d, "chunk_attention: rows too short for the heads");
   if (tokens == 0) return 0;
+  max_keys += max_keys & 1;            // the queries behind the page addresses start on a 16-byte boundary
   const size_t smem = (size_t)max_keys * sizeof(long long) + ((size_t)H * d + (size_t)(talk ? 2 : 1) * H * max_keys) * sizeof(float);
   PTL_REQUIRE(smem <= 200 * 1024, "chunk_attention: %d heads over %d keys do not fit the shared memory of a block (%zu bytes)", H,
               max_keys, smem);
   static SmemRaised raised = {};
   if (smem > 48 * 1024)
     if (int rc = raise_shared_memory("chunk_attention", chunk_attention_kernel<T>, 200 * 1024, raised)) return rc;
-  const int vec_ok = d % Vec16<T>::N == 0 && dv % Vec16<T>::N == 0 && aligned16(cache);   // every key row starts on a 16-byte boundary
+  const int vec_ok = d % Vec16<T>::N == 0 && dv % Vec16<T>::N == 0 && d % 4 == 0 && aligned16(cache);   // every key row starts on a 16-byte boundary
   return launch_kernel("chunk_attention", chunk_attention_kernel<T>, dim3(tokens), dim3(256), smem, as_stream(stream), (T*)out,
                        out_ld, column, (const T*)qkv, q_ld, q_bias, (const T*)cache, block_table, table_width, tok_req, positions,
                        H, G, d, dv, page_size, scale, chunk, r1, r2, talk, max_keys, num_pages, out_scale, vec_ok);
