@@ -177,8 +177,8 @@ class TibepelConfig:
             raise ConfigError(f"norm.eps must be positive, got {eps}")
         eos = data.get("eos_token_id")
         return cls(vocab=_positive_int(data, "vocab", ""), width=width, layers=tuple(layers),
-                   embedding_scale=float(_need(_need(data, "embedding", ""), "scale", "embedding.")),
-                   norm_eps=eps, logit_softcap=float(_need(data, "logit_softcap", "")),
+                   embedding_scale=float((data.get("embedding") or {}).get("scale", 1.0)),       # absent: rows as stored
+                   norm_eps=eps, logit_softcap=float(data.get("logit_softcap") or 0.0),          # absent or 0: no cap
                    side_dim=_positive_int(_need(data, "token_side", ""), "dim", "token_side."),
                    initializer_range=float(data.get("initializer_range", 0.02)),
                    eos_token_id=[int(e) for e in eos] if isinstance(eos, (list, tuple)) else eos)

@@ -47,10 +47,12 @@ kv_write_normed_kernel(T* __restrict__ cache, const T* __restrict__ qkv, const f
   }
 }
 
+constexpr int kMaxMixedHeads = 128;     // heads whose weights can be mixed (a thread holds one key's column of them)
+
 // One block per query token.  Keys j = lo .. p of the token's request, lo = p - p % chunk (0 without chunks):
 //   score_h(j) = (q_h + bias) . k_j * scale - r1[h] * log1p(r2[h] * (p - j));   w_h = softmax_j;
 //   w'_h = sum_g talk[h, g] w_g;   out_h = out_scale * sum_j w'_h(j) v_j.
-// Shared memory: max_keys page addresses, the query (H * d floats), one or two arrays of H * max_keys weights.
+// Shared memory: max_keys page addresses, the query (H * d floats), H * max_keys weights.
 template <typename T>
 __global__ void __launch_bounds__(256)
 chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __restrict__ qkv, int q_ld,
@@ -62,7 +64,6 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
   long long* page_at = reinterpret_cast<long long*>(smem_raw);       // first element of the page that holds key j, -1: none
   float* q = reinterpret_cast<float*>(page_at + max_keys);
   float* w = q + H * d;
-  float* mixed = w + (size_t)H * max_keys;
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -147,17 +148,20 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
     for (int j = lane; j < n; j += 32) wh[j] *= inv;
   }
   __syncthreads();
-  const float* use = w;
   if (talk) {
-    for (int i = threadIdx.x; i < H * n; i += blockDim.x) {
-      const int h = i / n, j = i % n;
-      float acc = 0.f;
-      for (int g = 0; g < H; ++g) acc = fmaf(talk[h * H + g], w[(size_t)g * max_keys + j], acc);
-      mixed[(size_t)h * max_keys + j] = acc;
+    // in place, a key's column of weights at a time: the thread that owns the key reads all heads' weights, then writes the mixed ones
+    for (int j = threadIdx.x; j < n; j += blockDim.x) {
+      float col[kMaxMixedHeads];
+      for (int g = 0; g < H; ++g) col[g] = w[(size_t)g * max_keys + j];
+      for (int h = 0; h < H; ++h) {
+        float acc = 0.f;
+        for (int g = 0; g < H; ++g) acc = fmaf(talk[h * H + g], col[g], acc);
+        w[(size_t)h * max_keys + j] = acc;
+      }
     }
     __syncthreads();
-    use = mixed;
   }
+  const float* use = w;
   // outputs: one (kv head, value element) pair per thread and turn, for up to four of the kv head's query heads at a
   // time, so that a value is fetched once for them; consecutive threads take consecutive elements
   for (int i = threadIdx.x; i < G * dv; i += blockDim.x) {
@@ -203,7 +207,8 @@ int chunk_attention(void* out, int out_ld, int column, const void* qkv, int q_ld
   PTL_REQUIRE(column >= 0 && column + H * dv <= out_ld && q_ld >= H * d, "chunk_attention: rows too short for the heads");
   if (tokens == 0) return 0;
   max_keys += max_keys & 1;            // the queries behind the page addresses start on a 16-byte boundary
-  const size_t smem = (size_t)max_keys * sizeof(long long) + ((size_t)H * d + (size_t)(talk ? 2 : 1) * H * max_keys) * sizeof(float);
+  PTL_REQUIRE(!talk || H <= kMaxMixedHeads, "chunk_attention: weights of at most %d heads can be mixed, got %d", kMaxMixedHeads, H);
+  const size_t smem = (size_t)max_keys * sizeof(long long) + ((size_t)H * d + (size_t)H * max_keys) * sizeof(float);
   PTL_REQUIRE(smem <= 200 * 1024, "chunk_attention: %d heads over %d keys do not fit the shared memory of a block (%zu bytes)", H,
               max_keys, smem);
   static SmemRaised raised = {};
