@@ -21,7 +21,7 @@ __global__ void causal_conv_kernel(T* __restrict__ out, const T* __restrict__ x,
                                    const float* __restrict__ w, const float* __restrict__ b, int taps,
                                    const float* __restrict__ state, const int* __restrict__ q_start,
                                    const int* __restrict__ tok_req, const int* __restrict__ positions,
-                                   const int* __restrict__ state_slot, int silu) {
+                                   const int* __restrict__ state_slot, int silu, float* __restrict__ state_out) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -33,6 +33,21 @@ __global__ void causal_conv_kernel(T* __restrict__ out, const T* __restrict__ x,
   const int pos = positions[t];
   const float* st = state + (size_t)state_slot[r] * (taps > 1 ? taps - 1 : 1) * channels;
   float acc = b ? b[c] : 0.f;
+  if (state_out) {
+    // every request brings one token: this thread is the only one that touches its channel of the request's state, so
+    // it also moves the state on (entry j takes entry j + 1, the last one the token's input)
+    float* so = state_out + (size_t)state_slot[r] * (taps - 1) * channels;
+    const float x_now = to_f32(x[(size_t)t * ld + column + c]);
+    for (int j = 0; j < taps - 1; ++j) {
+      const float v = pos - (taps - 1 - j) >= 0 ? st[(size_t)j * channels + c] : 0.f;
+      acc = fmaf(w[(size_t)c * taps + j], v, acc);
+      if (j > 0) so[(size_t)(j - 1) * channels + c] = v;
+    }
+    acc = fmaf(w[(size_t)c * taps + taps - 1], x_now, acc);
+    so[(size_t)(taps - 2) * channels + c] = x_now;
+    out[(size_t)t * channels + c] = from_f32<T>(silu ? silu_f32(acc) : acc);
+    return;
+  }
   for (int k = 0; k < taps; ++k) {
     const int back = taps - 1 - k;
     float v = 0.f;
@@ -327,17 +342,19 @@ gated_head_norm_kernel(T* __restrict__ out, int out_ld, int column, const float*
 template <typename T>
 int causal_conv(void* out, const void* x, int ld, int column, int channels, const float* w, const float* b, int taps, float* state,
                 const int* q_start, const int* tok_req, const int* positions, const int* state_slot, int tokens, int requests,
-                int silu, void* stream) {
+                int silu, int single_tokens, void* stream) {
   PTL_REQUIRE(tokens >= 0 && requests >= 0 && channels > 0 && taps > 0 && column >= 0 && column + channels <= ld,
               "causal_conv: bad sizes tokens=%d channels=%d taps=%d column=%d ld=%d", tokens, channels, taps, column, ld);
   if (tokens == 0) return 0;
   const dim3 block(128), tiles((channels + 127) / 128);
   PTL_REQUIRE(tiles.x <= 65535, "causal_conv: too many channels (%d)", channels);
+  // a step of single tokens (as many rows as requests, each request's rows being one): one kernel reads and moves the state
+  float* state_out = (single_tokens && taps > 1) ? state : nullptr;
   if (int rc = launch_kernel("causal_conv", causal_conv_kernel<T>, dim3(tokens, tiles.x), block, 0, as_stream(stream), (T*)out,
                              (const T*)x, ld, column, channels, w, b, taps, (const float*)state, q_start, tok_req, positions,
-                             state_slot, silu))
+                             state_slot, silu, state_out))
     return rc;
-  if (taps == 1 || requests == 0) return 0;
+  if (taps == 1 || requests == 0 || state_out) return 0;
   return launch_kernel("conv_state", conv_state_kernel<T>, dim3(requests, tiles.x), block, 0, as_stream(stream), state, (const T*)x,
                        ld, column, channels, taps, q_start, positions, state_slot);
 }
@@ -408,9 +425,9 @@ int gated_head_norm(void* out, int out_ld, int column, const float* o, const flo
   PTL_EXPORT int ptl_causal_conv##SUFFIX(void* out, const void* x, int ld, int column, int channels, const float* w,               \
                                          const float* b, int taps, float* state, const int* q_start, const int* tok_req,           \
                                          const int* positions, const int* state_slot, int tokens, int requests, int silu,         \
-                                         void* stream) {                                                                          \
+                                         int single_tokens, void* stream) {                                                       \
     return ptl::causal_conv<TYPE>(out, x, ld, column, channels, w, b, taps, state, q_start, tok_req, positions, state_slot, tokens, \
-                                  requests, silu, stream);                                                                        \
+                                  requests, silu, single_tokens, stream);                                                         \
   }                                                                                                                               \
   PTL_EXPORT int ptl_selective_scan##SUFFIX(void* out, const void* xc, const float* dt_raw, const float* dt_bias, const float* A,  \
                                             const void* bc, const float* D, const void* z, int z_ld, int z_column, int inner,      \

@@ -33,7 +33,7 @@ _SIGNATURES = {
     "ptl_clamped_glu": [_ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _c_f, _c_f, _ptr],
     "ptl_token_side": [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr],
     "ptl_causal_conv": [_ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int,
-                        _c_int, _ptr],
+                        _c_int, _c_int, _ptr],
     "ptl_selective_scan": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _ptr, _ptr,
                            _c_int, _ptr],
     "ptl_gated_delta_rule": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_f,
@@ -882,10 +882,13 @@ class CudaOps:
         if w.shape[0] != channels or state.shape[1] != max(taps - 1, 1) or state.shape[2] != channels:
             raise KernelError(f"causal_conv: weight {list(w.shape)} and state {list(state.shape)} do not fit {channels} channels")
         out = self.empty((x.shape[0], channels), x.dtype)
+        # a step in which every request brings one token (a captured decode step has as many rows as requests, padding
+        # included): the kernel that convolves also moves the state on
+        single = int(getattr(ctx, "max_q_len", 0) == 1)
         fn = getattr(self.lib, "ptl_causal_conv" + _suffix(x.dtype))
         self._check(fn(_p(out), _p(x), x.shape[1], int(column), int(channels), _p(w), _p(b), taps, _p(state), _p(ctx.q_start),
                        _p(ctx.tok_req), _p(ctx.positions), _p(ctx.state_slot), x.shape[0], ctx.num_requests, int(bool(silu)),
-                       self._stream()), kernels=2 if taps > 1 else 1)
+                       single, self._stream()), kernels=2 if taps > 1 and not single else 1)
         return out
 
     def selective_scan(self, xc: torch.Tensor, dt: torch.Tensor, dt_b: torch.Tensor, A: torch.Tensor, bc: torch.Tensor,

@@ -34,7 +34,7 @@ def _ctx(q_lens, starts, slots, device):
     q_start = [0]
     for n in q_lens:
         q_start.append(q_start[-1] + n)
-    return SimpleNamespace(num_requests=len(q_lens), num_tokens=q_start[-1], q_start=t(q_start), state_slot=t(slots),
+    return SimpleNamespace(num_requests=len(q_lens), num_tokens=q_start[-1], q_start=t(q_start), state_slot=t(slots), max_q_len=max(q_lens),
                            tok_req=t([r for r, n in enumerate(q_lens) for _ in range(n)]),
                            positions=t([s + i for s, n in zip(starts, q_lens) for i in range(n)]))
 
@@ -60,9 +60,14 @@ def _close(got, ref, dtype, what, scale=None):
 STEP = ([5, 1, 2, 9], [0, 17, 3, 0], [2, 0, 3, 1])      # a fresh portion, a single token, two tokens of a running request, a fresh one
 
 
+SINGLE_TOKENS = ([1, 1, 1, 1], [0, 17, 2, 1], [2, 0, 3, 1])       # a decode step: the first tokens of a request among them
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("step", [STEP, SINGLE_TOKENS], ids=["mixed", "single"])
 @pytest.mark.parametrize("taps,channels", [(4, 40), (2, 129), (5, 8), (1, 16)])
-def test_causal_conv_and_its_state(ops, dtype, taps, channels):
+def test_causal_conv_and_its_state(ops, dtype, taps, channels, step):
+    STEP = step
     g = torch.Generator().manual_seed(taps * 100 + channels)
     T = sum(STEP[0])
     tensors = {"x": torch.randn(T, channels + 7, generator=g).to(DTYPES[dtype]), "w": torch.randn(channels, taps, generator=g),
@@ -304,6 +309,59 @@ def test_steps_from_captured_graphs(folders, dtype):
             assert any(isinstance(k, tuple) for k in llm.engine._graphs)
     if dtype == "float32":
         assert outs[True] == outs[False] and outs[True][0] == outs[True][2]
+
+
+def _random_config(seed):
+    """Sizes drawn freely: odd head sizes, one to three kv heads, blocks of 3 to 50 positions, 1 to 5 taps, 1 to 40
+    states, layers with and without a feed-forward, in any order."""
+    rng = random.Random(seed)
+    width = rng.choice([48, 56, 64, 72, 88, 104, 136])
+    layers = []
+    for i in range(rng.randint(2, 4)):
+        mlp = plain.dense(rng.randint(8, 150), rng.choice([0.5, 1.0, 2.0, 7.0])) if rng.random() < 0.7 else None
+        if (i + seed) % 2 == 0:
+            layers.append(plain.layer("mamba1", plain.scan(rng.randint(8, 100), rng.randint(1, 40), rng.randint(1, 12), rng.randint(1, 5)), mlp))
+        else:
+            kv, kv2 = rng.randint(1, 3), rng.randint(1, 3)
+            a = plain.left(kv * rng.choice([1, 2, 4]), kv, rng.randint(4, 72), rng.randint(4, 72), rng.randint(3, 50), rng.uniform(0.05, 0.4))
+            b = plain.right(kv2 * rng.choice([1, 2, 3]), kv2, rng.randint(4, 70), rng.randint(4, 70), rng.randint(1, 5))
+            layers.append(plain.layer("parallel", plain.parallel(a, b, rng.uniform(0.2, 1.5), rng.uniform(0.2, 1.5)), mlp))
+    return plain.config(rng.randint(50, 300), width, rng.randint(1, 9), layers, scale=rng.uniform(1.0, 6.0),
+                        eps=rng.choice([1e-6, 1e-5, 1e-3]), cap=rng.choice([8.0, 30.0]))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("seed", range(8))
+def test_random_configurations(tmp_path, dtype, seed):
+    cfg = _random_config(seed)
+    plain.write_model(tmp_path, cfg, 100 + seed, DTYPES[dtype])
+    rng = random.Random(seed)
+    seqs = {f"s{i}": random_tokens(n, cfg["vocab"], 10 * seed + i) for i, n in enumerate([rng.randint(1, 120) for _ in range(5)])}
+    ref = _reference(tmp_path, seqs)
+    # Drawn weights now and then put a row next to a clamp's or a sharp softmax's edge, where float32 rounding alone
+    # moves the logits of that row and the following ones by 6e-4: the plain implementation run in float32 tells how
+    # much a request can take; a wrong mechanism moves far more.
+    plain.F = torch.float32
+    try:
+        low = _reference(tmp_path, seqs)
+    finally:
+        plain.F = torch.float64
+    inherent = {r: float((low[r].double() - ref[r]).abs().max()) for r in seqs}
+    page = rng.choice([4, 8, 16, 32])
+    for family in (traces.whole, traces.mixed):
+        steps = family(seqs)
+        eng = _engine(tmp_path, dtype, page, -(-traces.max_live_tokens(steps, 32) // page) + 4)
+        got = traces.replay(eng, steps)
+        for r in seqs:
+            err = (got[r].double() - ref[r]).abs().max(-1).values
+            if dtype == "float32":
+                assert err.max() < max(5e-4, 4 * inherent[r]), (seed, family.__name__, r, float(err.max()), inherent[r], cfg)
+            else:
+                diff = got[r].double() - ref[r]
+                rms = (diff - diff.mean(-1, keepdim=True)).pow(2).mean(-1).sqrt() / ref[r].std()
+                assert rms.mean() < 0.05 and rms.kthvalue(max(1, int(0.9 * rms.numel()))).values < 0.15, \
+                    (seed, family.__name__, r, float(rms.mean()), float(rms.max()))
+        eng.check_device_status()
 
 
 @pytest.mark.parametrize("seed", [1, 2])
