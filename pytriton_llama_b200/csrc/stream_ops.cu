@@ -95,7 +95,8 @@ token_side_kernel(float* __restrict__ residual, const T* __restrict__ x, const f
     }
   }
   __syncthreads();
-  for (int j = warp; j < dim; j += nwarps) {
+#pragma unroll (TPB == 1 ? 4 : 1)
+  for (int j = warp; j < dim; j += nwarps) {       // (few tokens: four rows per turn, their packets fetched side by side)
     const T* wr = w_gate + (size_t)j * width;
     float acc[TPB];
 #pragma unroll
@@ -136,6 +137,7 @@ token_side_kernel(float* __restrict__ residual, const T* __restrict__ x, const f
   float ss[TPB];
 #pragma unroll
   for (int k = 0; k < TPB; ++k) ss[k] = 0.f;
+#pragma unroll (TPB == 1 ? 4 : 1)
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     const T* wr = w_proj + (size_t)i * dim;
     float acc[TPB];
