@@ -170,8 +170,8 @@ def _tibepel(width, layers, ff, vocab):
 
 
 def family_bench(args) -> int:
-    """``--family tibepel``: prefill (one step of 2,048 prompt tokens) and decode (8 requests at 1,024 tokens, a step
-    with its sampling kernel) of the Tibepel decoder and of a Llama decoder of the same width, depth, feed-forward size
+    """``--family tibepel``: prefill (one step of 2,048 prompt tokens, as one prompt and as 8 prompts of 256) and decode
+    (8 requests at 1,024 tokens, a step with its sampling kernel) of the Tibepel decoder and of a Llama decoder of the same width, depth, feed-forward size
     and vocabulary, on random weights, timed with CUDA events after warm-up; then one timed step of each kind with
     every operator bracketed by events, for the milliseconds by class of kernels.  One JSON line."""
     import torch
@@ -215,6 +215,17 @@ def family_bench(args) -> int:
             for _ in range(3):
                 prefill()
             prefill_ms = statistics.median(timed(prefill, 1) for _ in range(5))
+            # the same number of prompt tokens as 8 prompts of 256 in one step (mixers that walk a request's tokens in
+            # order work on the 8 requests side by side)
+            parts = [toks(prompt_len // 8) for _ in range(8)]
+
+            def prefill_split():
+                engine.step([StepEntry(f"p{i}", t, [len(t) - 1]) for i, t in enumerate(parts)])
+                for i in range(8):
+                    engine.finish(f"p{i}")
+            for _ in range(3):
+                prefill_split()
+            prefill_split_ms = statistics.median(timed(prefill_split, 1) for _ in range(5))
             reqs = [f"d{i}" for i in range(batch)]
             for r in reqs:
                 engine.step([StepEntry(r, toks(context), [])])
@@ -237,6 +248,8 @@ def family_bench(args) -> int:
             decode_classes = engine.step([StepEntry(r, f, [0]) for r, f in zip(reqs, feed)]).kernel_ms
             params = sum(t.numel() for t in _tensors_of(engine))
             row[name] = {"prefill_tokens_per_s": round(prompt_len / prefill_ms * 1e3, 1), "prefill_ms": round(prefill_ms, 3),
+                         "prefill_8x256_tokens_per_s": round(prompt_len / prefill_split_ms * 1e3, 1),
+                         "prefill_8x256_ms": round(prefill_split_ms, 3),
                          "decode_tokens_per_s": round(batch / decode_ms * 1e3, 1), "decode_ms_per_step": round(decode_ms, 4),
                          "decode_launches_per_step": int(launches), "weights_gb": round(params * (4 if args.dtype == "float32" else 2) / 1e9, 3),
                          "decode_hbm_frac": round(params * (4 if args.dtype == "float32" else 2) / (decode_ms * 1e-3) / 1e9 / peaks["hbm_gbs"], 4),
