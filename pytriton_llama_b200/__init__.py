@@ -1,12 +1,13 @@
-"""A single-GPU inference engine for the dense GQA Llama decoder, written for NVIDIA B200
-(sm_100a): typed configuration and registry, safetensors weights, a decoder put together from
+"""A single-GPU inference engine for the dense GQA Llama decoder and for the Tibepel decoder
+(selective-scan layers, and attention in blocks of positions beside a gated delta rule), written
+for NVIDIA B200 (sm_100a): typed configuration and registry, safetensors weights, a decoder put together from
 parts, a paged cache, one step function for mixed batches, a scheduler, sampling, and
 hand-written CUDA kernels loaded from ``csrc/``.
 """
-from .config import EngineConfig, LlamaConfig  # noqa: F401
+from .config import EngineConfig, LlamaConfig, TibepelConfig  # noqa: F401
 from .sampling import SamplingParams  # noqa: F401
 
-__all__ = ["EngineConfig", "LlamaConfig", "SamplingParams", "LLM", "Engine", "StepEntry",
+__all__ = ["EngineConfig", "LlamaConfig", "TibepelConfig", "SamplingParams", "LLM", "Engine", "StepEntry",
            "GenerateText", "GenerateStreamText"]
 
 
