@@ -173,15 +173,18 @@ selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float
 // Per value head h (query/key head c = h / (heads / kv_heads)) and token, with k, q scaled to unit length
 // (q also by q_scale), beta = sigmoid(b), g = exp(-rate[h] * softplus(a + dt_bias[h])):
 //     S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q.
-// A column S[:, j] is independent of the others: eight lanes share a column, lane l holding rows l, l + 8, ...
-// (RPL of them); a block of 128 threads walks 16 columns of one head of one request through its tokens.
+// A column S[:, j] is independent of the others: eight lanes share a column, lane l holding the row pairs
+// (16 m + 2 l, 16 m + 2 l + 1), m = 0 .. RPL / 2 - 1, as float2 values, so that the products, decays and updates of a
+// token are the two-wide float32 instructions of sm_100 (__ffma2_rn and __fmul2_rn round each half like the scalar
+// forms) and k and q come from shared memory as 8-byte packets.  A block of 128 threads walks 16 columns of one head of
+// one request through its tokens.
 // The tokens come in batches of kDeltaBatch.  All threads bring a batch's q and k of the head (once, not once per
 // column), its 16 values, gates and decays into shared memory, and hold the next batch's q and k in registers while the
 // current one is walked, so that the walk, whose steps depend on one another, never waits for global memory.  The unit
 // scaling is folded into the walk: with kn = 1 / |k| and qn = q_scale / |q|,
 //     dot = kn * (S^T k);  u = beta (v - dot);  S <- S + k (kn u);  o = qn * (S^T q).
 // qkv rows: [q: kv_heads * d | k: kv_heads * d | v: heads * dv];  ba rows: [b: heads | a: heads] float32.
-// Shared memory: kDeltaBatch * (2 * d + 16 + 4) floats.
+// Shared memory: kDeltaBatch * (2 * 8 * RPL + 16 + 4) floats; rows of q and k are 8 * RPL floats apart, zero beyond d.
 constexpr int kDeltaBatch = 16;
 
 template <typename T, int RPL>
@@ -190,10 +193,13 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
                         const float* __restrict__ rate, const float* __restrict__ dt_bias, float* __restrict__ state,
                         const int* __restrict__ q_start, const int* __restrict__ positions, const int* __restrict__ state_slot,
                         int heads, int kv_heads, int d, int dv, float unit_eps, float q_scale) {
+  static_assert(RPL % 2 == 0, "a lane holds pairs of rows");
+  constexpr int DS = 8 * RPL;                       // floats between rows of q and k in shared memory
+  constexpr int HP = RPL / 2;                       // row pairs of a lane
   extern __shared__ __align__(16) float delta_smem[];
-  float* s_q = delta_smem;                         // [batch][d], as projected
-  float* s_k = s_q + kDeltaBatch * d;
-  float* s_v = s_k + kDeltaBatch * d;              // [batch][16]
+  float* s_q = delta_smem;                         // [batch][DS], as projected
+  float* s_k = s_q + kDeltaBatch * DS;
+  float* s_v = s_k + kDeltaBatch * DS;             // [batch][16]
   float* s_beta = s_v + kDeltaBatch * 16;
   float* s_g = s_beta + kDeltaBatch;
   float* s_qn = s_g + kDeltaBatch;
@@ -212,16 +218,22 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
   const int ld = 2 * kv_heads * d + heads * dv;
   float* st = state + (((size_t)state_slot[r] * heads + h) * d) * dv + j;
   const bool from_zero = positions[lo] == 0;
-  float S[RPL];
+  float2 S[HP];
 #pragma unroll
-  for (int i = 0; i < RPL; ++i) {
-    const int row = sub + 8 * i;
-    S[i] = (row < d && !from_zero) ? st[(size_t)row * dv] : 0.f;
+  for (int m = 0; m < HP; ++m) {
+    const int row = 16 * m + 2 * sub;
+    S[m].x = (row < d && !from_zero) ? st[(size_t)row * dv] : 0.f;
+    S[m].y = (row + 1 < d && !from_zero) ? st[(size_t)(row + 1) * dv] : 0.f;
   }
+  for (int i = threadIdx.x; i < 2 * kDeltaBatch * DS; i += blockDim.x) s_q[i] = 0.f;   // (s_k follows s_q) zero beyond d for good
   const float rate_h = rate[h], bias_h = dt_bias[h];
   // Element i of a thread's share of a batch: flat index threadIdx.x + 128 * i over [batch][d]; RPL of them cover
   // kDeltaBatch * d = 16 d <= 128 * RPL (d <= 8 * RPL).  (token, element) of the flat index advance without a division.
-  float pq[RPL], pk[RPL];
+  // They are kept as fetched (T, not float): a conversion right behind its load would hold the warp until the load has
+  // come back, and the point is to have the loads in flight during the walk.  The same for the batch's 16 x 16 values
+  // (two per thread) and a token's two gate inputs.
+  T pq[RPL], pk[RPL], pv[2];
+  float pb = 0.f, pa = 0.f;
   const int tok_first = threadIdx.x / d, e_first = threadIdx.x % d, tok_step = 128 / d, e_step = 128 % d;
   auto fetch = [&](int t0) {
     const int nb = min(kDeltaBatch, hi - t0);
@@ -230,75 +242,105 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
     for (int i = 0; i < RPL; ++i) {
       if (tok < nb) {
         const T* row = qkv + (size_t)(t0 + tok) * ld;
-        pq[i] = to_f32(row[c * d + e]);
-        pk[i] = to_f32(row[(kv_heads + c) * d + e]);
+        pq[i] = row[c * d + e];
+        pk[i] = row[(kv_heads + c) * d + e];
       }
       tok += tok_step;
       e += e_step;
       if (e >= d) { e -= d; ++tok; }
     }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = threadIdx.x + 128 * i;
+      if ((idx >> 4) < nb) pv[i] = qkv[(size_t)(t0 + (idx >> 4)) * ld + 2 * kv_heads * d + h * dv + min(j0 + (idx & 15), dv - 1)];
+    }
+    if (threadIdx.x < nb) {
+      pb = ba[(size_t)(t0 + threadIdx.x) * 2 * heads + h];
+      pa = ba[(size_t)(t0 + threadIdx.x) * 2 * heads + heads + h];
+    }
   };
   fetch(lo);
   for (int t0 = lo; t0 < hi; t0 += kDeltaBatch) {
     const int nb = min(kDeltaBatch, hi - t0);
-    __syncthreads();                                  // the batch before has been walked
+    __syncthreads();                                  // the batch before has been walked (and the rows are zeroed)
+    {
+      int tok = tok_first, e = e_first;
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      const int idx = threadIdx.x + 128 * i;
-      if (idx < nb * d) { s_q[idx] = pq[i]; s_k[idx] = pk[i]; }
+      for (int i = 0; i < RPL; ++i) {
+        if (tok < nb) { s_q[tok * DS + e] = to_f32(pq[i]); s_k[tok * DS + e] = to_f32(pk[i]); }
+        tok += tok_step;
+        e += e_step;
+        if (e >= d) { e -= d; ++tok; }
+      }
     }
-    for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) {
-      const int tok = i >> 4;
-      s_v[i] = to_f32(qkv[(size_t)(t0 + tok) * ld + 2 * kv_heads * d + h * dv + min(j0 + (i & 15), dv - 1)]);
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = threadIdx.x + 128 * i;
+      if ((idx >> 4) < nb) s_v[idx] = to_f32(pv[i]);
     }
     if (threadIdx.x < nb) {
-      const float* row = ba + (size_t)(t0 + threadIdx.x) * 2 * heads;
-      s_beta[threadIdx.x] = 1.0f / (1.0f + expf(-row[h]));
-      s_g[threadIdx.x] = expf(-rate_h * softplus_f32(row[heads + h] + bias_h));
+      s_beta[threadIdx.x] = 1.0f / (1.0f + expf(-pb));
+      s_g[threadIdx.x] = expf(-rate_h * softplus_f32(pa + bias_h));
     }
     __syncthreads();
     if (t0 + kDeltaBatch < hi) fetch(t0 + kDeltaBatch);   // in flight while this batch is walked
-    for (int tok = warp; tok < nb; tok += 4) {           // a warp per token: the lengths of q and k
-      float qq = 0.f, kk = 0.f;
-      for (int e = lane; e < d; e += 32) {
-        qq = fmaf(s_q[tok * d + e], s_q[tok * d + e], qq);
-        kk = fmaf(s_k[tok * d + e], s_k[tok * d + e], kk);
+    {
+      // the lengths of q and k: warp w takes tokens w, w + 4, w + 8, w + 12, their eight sums over the lanes side by side
+      float qq[4] = {0.f, 0.f, 0.f, 0.f}, kk[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const int tok = warp + 4 * m;
+        if (tok < nb)
+          for (int e = lane; e < d; e += 32) {
+            qq[m] = fmaf(s_q[tok * DS + e], s_q[tok * DS + e], qq[m]);
+            kk[m] = fmaf(s_k[tok * DS + e], s_k[tok * DS + e], kk[m]);
+          }
       }
-      qq = warp_sum(qq);
-      kk = warp_sum(kk);
-      if (lane == 0) {
-        s_qn[tok] = q_scale / sqrtf(qq + unit_eps);
-        s_kn[tok] = 1.0f / sqrtf(kk + unit_eps);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+#pragma unroll
+        for (int m = 0; m < 4; ++m) {
+          qq[m] += __shfl_xor_sync(0xffffffffu, qq[m], o);
+          kk[m] += __shfl_xor_sync(0xffffffffu, kk[m], o);
+        }
+      }
+#pragma unroll
+      for (int m = 0; m < 4; ++m) {
+        const int tok = warp + 4 * m;
+        if (lane == 0 && tok < nb) {
+          s_qn[tok] = q_scale / sqrtf(qq[m] + unit_eps);
+          s_kn[tok] = 1.0f / sqrtf(kk[m] + unit_eps);
+        }
       }
     }
     __syncthreads();
 #pragma unroll (RPL <= 16 ? 2 : 1)
     for (int tok = 0; tok < nb; ++tok) {      // (two tokens per turn: the read-out of one overlaps the update of the next)
-      const float* kp = s_k + tok * d;
-      const float* qp = s_q + tok * d;
+      const float2* kp = reinterpret_cast<const float2*>(s_k + tok * DS) + sub;     // pair m of this lane: kp[8 * m]
+      const float2* qp = reinterpret_cast<const float2*>(s_q + tok * DS) + sub;
       const float g = s_g[tok], kn = s_kn[tok];
-      float k[RPL];
-      float dot0 = 0.f, dot1 = 0.f;
+      const float2 g2 = make_float2(g, g);
+      float2 k[HP];
+      float2 dot0 = make_float2(0.f, 0.f), dot1 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int i = 0; i < RPL; ++i) {
-        const int e = sub + 8 * i;
-        k[i] = e < d ? kp[e] : 0.f;
-        S[i] *= g;
-        if (i & 1) dot1 = fmaf(S[i], k[i], dot1); else dot0 = fmaf(S[i], k[i], dot0);
+      for (int m = 0; m < HP; ++m) {
+        k[m] = kp[8 * m];
+        S[m] = __fmul2_rn(S[m], g2);
+        if (m & 1) dot1 = __ffma2_rn(S[m], k[m], dot1); else dot0 = __ffma2_rn(S[m], k[m], dot0);
       }
-      float dot = dot0 + dot1;
+      float dot = (dot0.x + dot0.y) + (dot1.x + dot1.y);
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o);
       const float u = s_beta[tok] * (s_v[tok * 16 + grp] - kn * dot) * kn;
-      float acc0 = 0.f, acc1 = 0.f;
+      const float2 u2 = make_float2(u, u);
+      float2 acc0 = make_float2(0.f, 0.f), acc1 = make_float2(0.f, 0.f);
 #pragma unroll
-      for (int i = 0; i < RPL; ++i) {
-        const int e = sub + 8 * i;
-        S[i] = fmaf(k[i], u, S[i]);
-        const float qv = e < d ? qp[e] : 0.f;
-        if (i & 1) acc1 = fmaf(S[i], qv, acc1); else acc0 = fmaf(S[i], qv, acc0);
+      for (int m = 0; m < HP; ++m) {
+        S[m] = __ffma2_rn(k[m], u2, S[m]);
+        const float2 qv = qp[8 * m];
+        if (m & 1) acc1 = __ffma2_rn(S[m], qv, acc1); else acc0 = __ffma2_rn(S[m], qv, acc0);
       }
-      float acc = acc0 + acc1;
+      float acc = (acc0.x + acc0.y) + (acc1.x + acc1.y);
 #pragma unroll
       for (int o = 1; o < 8; o <<= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (sub == 0 && live) out[(size_t)(t0 + tok) * heads * dv + h * dv + j] = acc * s_qn[tok];
@@ -306,9 +348,10 @@ gated_delta_rule_kernel(float* __restrict__ out, const T* __restrict__ qkv, cons
   }
   if (live) {
 #pragma unroll
-    for (int i = 0; i < RPL; ++i) {
-      const int row = sub + 8 * i;
-      if (row < d) st[(size_t)row * dv] = S[i];
+    for (int m = 0; m < HP; ++m) {
+      const int row = 16 * m + 2 * sub;
+      if (row < d) st[(size_t)row * dv] = S[m].x;
+      if (row + 1 < d) st[(size_t)(row + 1) * dv] = S[m].y;
     }
   }
 }
@@ -393,8 +436,8 @@ int gated_delta_rule(float* out, const void* qkv, const float* ba, const float* 
   PTL_REQUIRE(requests <= 65535 && heads <= 65535, "gated_delta_rule: at most 65535 requests and heads");
   if (requests == 0) return 0;
   const dim3 grid((dv + 15) / 16, heads, requests), block(128);
-  const size_t smem = (size_t)kDeltaBatch * (2 * d + 16 + 4) * sizeof(float);     // at most 34 KB
-#define PTL_DELTA(RPL) return launch_kernel("gated_delta_rule", gated_delta_rule_kernel<T, RPL>, grid, block, smem, as_stream(stream), \
+#define PTL_DELTA(RPL) return launch_kernel("gated_delta_rule", gated_delta_rule_kernel<T, RPL>, grid, block, \
+    (size_t)kDeltaBatch * (2 * 8 * RPL + 16 + 4) * sizeof(float) /* at most 34 KB */, as_stream(stream), \
     out, (const T*)qkv, ba, rate, dt_bias, state, q_start, positions, state_slot, heads, kv_heads, d, dv, unit_eps, q_scale)
   const int per_lane = (d + 7) / 8;
   if (per_lane <= 2) PTL_DELTA(2);
