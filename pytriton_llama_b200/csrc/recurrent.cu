@@ -126,7 +126,11 @@ selective_scan_kernel(T* __restrict__ out, const T* __restrict__ xc, const float
   for (int t0 = lo; t0 < hi; t0 += tb) {
     const int nb = min(tb, hi - t0);
     __syncthreads();                                  // the batch before has been walked and written out
+    // (the turns of these two loops are unrolled so that a thread's loads are issued together: a conversion right
+    // behind its load holds the warp until the load has come back)
+#pragma unroll 8
     for (int i = threadIdx.x; i < nb * 2 * n_state; i += blockDim.x) s_bc[i] = to_f32(bc[(size_t)t0 * 2 * n_state + i]);
+#pragma unroll 4
     for (int i = threadIdx.x; i < nb * 16; i += blockDim.x) {
       const int tok = i >> 4, ch = min(c0 + (i & 15), inner - 1);
       const size_t row = (size_t)(t0 + tok);
