@@ -174,8 +174,10 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll 4
       for (int j = 0; j < n; ++j) {                   // (four keys per turn: their values are fetched side by side)
-        if (page_at[j] < 0) continue;
-        const float v = to_f32(cache[(size_t)page_at[j] + head_off + (size_t)((lo + j) % page_size) * dv]);
+        // no branch in here: a key without a page (its weight is zero already) reads the first page's value
+        const long long pg = page_at[j];
+        const T raw = cache[(size_t)(pg < 0 ? 0 : pg) + head_off + (size_t)((lo + j) % page_size) * dv];
+        const float v = pg < 0 ? 0.f : to_f32(raw);
 #pragma unroll
         for (int a4 = 0; a4 < 4; ++a4)
           if (a4 < nh) acc[a4] = fmaf(w0[(size_t)a4 * max_keys + j], v, acc[a4]);

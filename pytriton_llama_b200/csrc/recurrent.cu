@@ -37,7 +37,30 @@ __global__ void causal_conv_kernel(T* __restrict__ out, const T* __restrict__ x,
     // every request brings one token: this thread is the only one that touches its channel of the request's state, so
     // it also moves the state on (entry j takes entry j + 1, the last one the token's input)
     float* so = state_out + (size_t)state_slot[r] * (taps - 1) * channels;
-    const float x_now = to_f32(x[(size_t)t * ld + column + c]);
+    const T x_raw = x[(size_t)t * ld + column + c];
+    constexpr int kHeld = 7;                          // up to 8 taps: the entries are all read before any is written
+    if (taps - 1 <= kHeld) {
+      float v[kHeld], wt[kHeld];
+#pragma unroll
+      for (int j = 0; j < kHeld; ++j) {
+        const bool there = j < taps - 1;
+        v[j] = (there && pos - (taps - 1 - j) >= 0) ? st[(size_t)j * channels + c] : 0.f;
+        wt[j] = there ? w[(size_t)c * taps + j] : 0.f;
+      }
+      const float x_now = to_f32(x_raw);
+#pragma unroll
+      for (int j = 0; j < kHeld; ++j) {
+        if (j < taps - 1) {
+          acc = fmaf(wt[j], v[j], acc);
+          if (j > 0) so[(size_t)(j - 1) * channels + c] = v[j];
+        }
+      }
+      acc = fmaf(w[(size_t)c * taps + taps - 1], x_now, acc);
+      so[(size_t)(taps - 2) * channels + c] = x_now;
+      out[(size_t)t * channels + c] = from_f32<T>(silu ? silu_f32(acc) : acc);
+      return;
+    }
+    const float x_now = to_f32(x_raw);
     for (int j = 0; j < taps - 1; ++j) {
       const float v = pos - (taps - 1 - j) >= 0 ? st[(size_t)j * channels + c] : 0.f;
       acc = fmaf(w[(size_t)c * taps + j], v, acc);
@@ -376,9 +399,11 @@ gated_head_norm_kernel(T* __restrict__ out, int out_ld, int column, const float*
   const int t = (int)(item / heads), h = (int)(item % heads);
   const float* src = o + (size_t)t * heads * dv + (size_t)h * dv;
   float ss = 0.f;
+#pragma unroll 4
   for (int e = lane; e < dv; e += 32) ss = fmaf(src[e], src[e], ss);
   ss = warp_sum(ss);
   const float rrms = 1.0f / sqrtf(ss / (float)dv + eps);
+#pragma unroll 4
   for (int e = lane; e < dv; e += 32) {
     const float g = to_f32(gate[(size_t)t * gate_ld + gate_column + h * dv + e]);
     out[(size_t)t * out_ld + column + h * dv + e] = from_f32<T>(src[e] * rrms * w[e] * silu_f32(g) * scale);

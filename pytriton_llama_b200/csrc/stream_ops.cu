@@ -84,7 +84,8 @@ token_side_kernel(float* __restrict__ residual, const T* __restrict__ x, const f
   const int nt = min(TPB, n_tokens - t0);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   for (int k = 0; k < TPB; ++k) {
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+#pragma unroll 4
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {      // (four turns' loads are issued together)
       float v = 0.f;
       if (k < nt) {
         v = residual[(size_t)(t0 + k) * width + i];
@@ -171,6 +172,7 @@ token_side_kernel(float* __restrict__ residual, const T* __restrict__ x, const f
     const float total = block_sum(ss[k], red);
     if (k >= nt) continue;
     const float rrms = 1.0f / sqrtf(total / (float)width + eps);
+#pragma unroll 4
     for (int i = threadIdx.x; i < width; i += blockDim.x)
       residual[(size_t)(t0 + k) * width + i] = s[(size_t)k * width + i] + y[(size_t)k * width + i] * rrms * norm_w[i];
   }
