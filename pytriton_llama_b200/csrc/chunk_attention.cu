@@ -25,6 +25,7 @@ kv_write_normed_kernel(T* __restrict__ cache, const T* __restrict__ qkv, const f
   const T* row = qkv + (size_t)t * ld;
   T* kp = cache + page * (size_t)G * page_size * (d + dv);
   T* vp = kp + (size_t)G * page_size * d;
+#pragma unroll 4
   for (int i = threadIdx.x; i < G * d; i += blockDim.x) {
     const int g = i / d, e = i % d;
     const float v = to_f32(row[H * d + i]) + (bias ? bias[H * d + i] : 0.f);
@@ -34,12 +35,14 @@ kv_write_normed_kernel(T* __restrict__ cache, const T* __restrict__ qkv, const f
   for (int g = warp; g < G; g += nwarps) {
     const int base = (H + G) * d + g * dv;
     float ss = 0.f;
+#pragma unroll 4
     for (int e = lane; e < dv; e += 32) {
       const float v = to_f32(row[base + e]) + (bias ? bias[base + e] : 0.f);
       ss = fmaf(v, v, ss);
     }
     ss = warp_sum(ss);
     const float f = eps > 0.f ? 1.0f / sqrtf(ss / (float)dv + eps) : 1.0f;
+#pragma unroll 4
     for (int e = lane; e < dv; e += 32) {
       const float v = to_f32(row[base + e]) + (bias ? bias[base + e] : 0.f);
       vp[((size_t)g * page_size + off) * dv + e] = from_f32<T>(v * f);
@@ -75,7 +78,8 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
   const int group = H / G;
   const size_t page_stride = (size_t)G * page_size * (d + dv);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  for (int i = threadIdx.x; i < H * d; i += blockDim.x)
+#pragma unroll 4
+  for (int i = threadIdx.x; i < H * d; i += blockDim.x)      // (four turns' loads are issued together)
     q[i] = to_f32(qkv[(size_t)t * q_ld + i]) + (q_bias ? q_bias[i] : 0.f);
   for (int j = threadIdx.x; j < n; j += blockDim.x) {
     const int pos = lo + j;
