@@ -98,7 +98,7 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
       if (there && vec_ok) {                            // 16-byte packets of the key row and of the queries
         constexpr int VN = Vec16<T>::N;
-#pragma unroll 4
+#pragma unroll 8
         for (int e = 0; e < d; e += VN) {
           const Vec16<T> kv = load16(kr + e);
 #pragma unroll
@@ -176,8 +176,8 @@ chunk_attention_kernel(T* __restrict__ out, int out_ld, int column, const T* __r
       const int nh = min(4, (c + 1) * group - h0);
       const float* w0 = use + (size_t)h0 * max_keys;
       float acc[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll 4
-      for (int j = 0; j < n; ++j) {                   // (four keys per turn: their values are fetched side by side)
+#pragma unroll 8
+      for (int j = 0; j < n; ++j) {                   // (eight keys per turn: their values are fetched side by side)
         // no branch in here: a key without a page (its weight is zero already) reads the first page's value
         const long long pg = page_at[j];
         const T raw = cache[(size_t)(pg < 0 ? 0 : pg) + head_off + (size_t)((lo + j) % page_size) * dv];

@@ -103,6 +103,7 @@ token_side_kernel(float* __restrict__ residual, const T* __restrict__ x, const f
 #pragma unroll
     for (int k = 0; k < TPB; ++k) acc[k] = 0.f;
     if (vec_ok) {
+#pragma unroll (TPB == 1 ? 4 : 1)
       for (int i = lane * VN; i < width; i += 32 * VN) {
         const Vec16<T> v = load16(wr + i);
 #pragma unroll
