@@ -364,6 +364,24 @@ def test_random_configurations(tmp_path, dtype, seed):
         eng.check_device_status()
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [50, 62])
+def test_widths_that_are_no_multiple_of_eight(tmp_path, dtype, width):
+    """No 16-byte packets anywhere: rows of the stream, of every weight and of the side table start at odd places."""
+    cfg = plain.config(77, width, 3, [
+        plain.layer("parallel", plain.parallel(plain.left(3, 1, 10, 14, 5, 0.3), plain.right(3, 3, 6, 10, 3), 0.8, 0.9), plain.dense(34, 2.0)),
+        plain.layer("mamba1", plain.scan(26, 3, 5, 4), plain.dense(18, 1.0)),
+    ], scale=2.0, cap=15.0)
+    plain.write_model(tmp_path, cfg, 3, DTYPES[dtype])
+    seqs = {"a": random_tokens(41, 77, 1), "b": random_tokens(9, 77, 2), "c": random_tokens(70, 77, 3)}
+    ref = _reference(tmp_path, seqs)
+    for family in (traces.whole, traces.mixed):
+        steps = family(seqs)
+        got = traces.replay(_engine(tmp_path, dtype, 8, -(-traces.max_live_tokens(steps, 32) // 8) + 4), steps)
+        for r in seqs:
+            _assert_logits(got[r], ref[r], dtype, f"width {width} {family.__name__} {r}")
+
+
 @pytest.mark.parametrize("seed", [1, 2])
 def test_random_traces_in_float32(folders, seed):
     folder = folders("Q", "float32")
