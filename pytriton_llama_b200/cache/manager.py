@@ -6,7 +6,8 @@ reserves a batch's whole life up front (lite_llama/executor/mem_manager.py:134-2
 lite_llama/generate.py:111-127); its request table gives each request a slot index
 (lite_llama/executor/req_tokens_table.py:15-29).  Here the unit is a page of ``page_size``
 tokens, pages are taken when a step needs them and given back when a request ends or, in a
-windowed group, when the window has passed them; the bookkeeping lives on the host.
+windowed group, when the window has passed them (but for the pages of the first positions where
+those stay visible); the bookkeeping lives on the host.
 
 Cache entries (one per run of a layer that stores keys and values) with equal needs form a
 group.  A page id is valid in every entry of its group: entry e keeps its share of page p in
@@ -126,8 +127,9 @@ class _Table:
     def array(self) -> np.ndarray:
         return self.pages[:self.n]
 
-    def held_below(self, block: int) -> int:
-        return int((self.pages[:min(block, self.n)] >= 0).sum()) if block > 0 else 0
+    def held_below(self, block: int, first: int = 0) -> int:
+        """Pages held in blocks ``first`` .. ``block`` - 1."""
+        return int((self.pages[first:min(block, self.n)] >= 0).sum()) if block > first else 0
 
 
 @dataclass
@@ -217,6 +219,12 @@ class CacheManager:
             return 0
         return first_key // self.page_size
 
+    def _kept_blocks(self, grp: CacheGroup) -> int:
+        """Blocks at the start of a request that are never given back: they hold positions that every
+        later query still sees (``CacheNeed.keep_first``)."""
+        keep = grp.need.keep_first if grp.need.kind == "window" else 0
+        return -(-keep // self.page_size) if keep > 0 else 0
+
     def pages_needed(self, req: Optional[Hashable], new_tokens: int, have_tokens: Optional[int] = None) -> Dict[int, int]:
         """Group -> pages that appending ``new_tokens`` would take, net of those the append gives back first."""
         if req is not None and req in self._requests:
@@ -233,7 +241,7 @@ class CacheManager:
             held = len(r.tables[gi]) if r else -(-have // self.page_size)
             need = total_blocks - held
             if r is not None and grp.need.kind in ("window", "chunk"):
-                need -= r.tables[gi].held_below(self._first_needed_block(grp, have))
+                need -= r.tables[gi].held_below(self._first_needed_block(grp, have), self._kept_blocks(grp))
             out[gi] = need
         return out
 
@@ -282,7 +290,7 @@ class CacheManager:
                 continue
             table = r.tables[gi]
             first = self._first_needed_block(grp, r.tokens)
-            for b in range(min(first, len(table))):
+            for b in range(self._kept_blocks(grp), min(first, len(table))):
                 if table[b] >= 0:
                     grp.pool.give_back(table[b])
                     table[b] = -1

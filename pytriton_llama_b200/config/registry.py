@@ -55,6 +55,9 @@ def _register_builtin() -> None:
     from .tibepel import TibepelConfig
     from ..models.tibepel import tibepel_spec
     register_architecture("Tibepel", TibepelConfig.from_dict, tibepel_spec)
+    from .lilenex import LilenexConfig
+    from ..models.lilenex import lilenex_spec
+    register_architecture("Lilenex", LilenexConfig.from_dict, lilenex_spec)
 
 
 _register_builtin()

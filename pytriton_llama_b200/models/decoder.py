@@ -71,12 +71,16 @@ class DecoderModel:
 
     # ------------------------------------------------------------------ cache
     def cache_entries(self) -> Dict[int, CacheNeed]:
-        """Cache entry id -> what the layer that writes it needs."""
+        """Cache entry id -> what the layers that use it need."""
         out: Dict[int, CacheNeed] = {}
         for e in self.spec.run_order:
             need = self.blocks[e.layer].cache_need()
             if e.cache in out and out[e.cache].group_key() != need.group_key():
-                raise ValueError(f"cache entry {e.cache} is used by layers with different needs")
+                try:        # (runs that only differ in how far back they look share what the farthest-looking needs)
+                    need = out[e.cache].merged(need)
+                except ValueError:
+                    raise ValueError(f"cache entry {e.cache} is used by layers with different needs") from None
+                out[e.cache] = need
             out.setdefault(e.cache, need)
         return out
 

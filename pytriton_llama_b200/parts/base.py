@@ -45,7 +45,7 @@ CATEGORIES = ("mixer", "ffn", "norm", "position", "token_input", "block")
 
 @dataclass(frozen=True)
 class TensorSpec:
-    shape: Tuple[int, ...]
+    shape: Tuple[int, ...]    # a negative entry -n: any size in the checkpoint, n when the tensor is drawn at random
     init: str = "normal"      # "normal": N(0, std) | "ones" | "ones_jitter": 1 + N(0, 0.01) | "zeros" | "uniform": U(lo, hi)
     optional: bool = False    # may be absent from the checkpoint (the part then gets None)
     lo: float = 0.0           # bounds of "uniform"
@@ -69,7 +69,8 @@ class CacheNeed:
     query lies in) or "none".  ``value_dim``: size of a value head where it differs from
     ``head_dim`` (0: the same).  ``state_shape``/``state_dtype``: per-request state of fixed size
     (None if none).  ``states``: further per-request states by name, float32, as (name, shape)
-    pairs; a mixer made of several lists those of all its members."""
+    pairs; a mixer made of several lists those of all its members.  ``keep_first`` (kind "window"):
+    the keys of positions below it stay visible, and held, whatever the window has passed."""
     kind: str = "none"
     kv_heads: int = 0
     head_dim: int = 0
@@ -78,6 +79,7 @@ class CacheNeed:
     state_dtype: Optional[torch.dtype] = None
     value_dim: int = 0
     states: Tuple[Tuple[str, Tuple[int, ...]], ...] = ()
+    keep_first: int = 0
 
     @property
     def v_dim(self) -> int:
@@ -85,7 +87,21 @@ class CacheNeed:
 
     def group_key(self):
         return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shape, self.state_dtype,
-                self.value_dim, self.states)
+                self.value_dim, self.states, self.keep_first)
+
+    def merged(self, other: "CacheNeed") -> "CacheNeed":
+        """The need of a cache entry that ``self`` and ``other`` both read: everything either of them
+        still sees is kept.  Raises where they differ in more than the window and the kept positions."""
+        from dataclasses import replace
+        if self.kind not in ("full", "window") or other.kind not in ("full", "window"):
+            if self.group_key() == other.group_key():
+                return self
+            raise ValueError("cache needs of this kind cannot be merged")
+        if replace(self, kind="full", window=0, keep_first=0).group_key() != replace(other, kind="full", window=0, keep_first=0).group_key():
+            raise ValueError("layers that share a cache entry differ in head counts, head sizes or states")
+        if self.kind == "full" or other.kind == "full":
+            return replace(self, kind="full", window=0, keep_first=0)
+        return replace(self, window=max(self.window, other.window), keep_first=max(self.keep_first, other.keep_first))
 
 
 @dataclass

@@ -41,7 +41,7 @@ def check_tensors(expected: Dict[str, TensorSpec], found: Dict[str, torch.Tensor
     for n, s in expected.items():
         if n in found:
             t = found[n]
-            if tuple(t.shape) != tuple(s.shape):
+            if len(t.shape) != len(s.shape) or any(w >= 0 and w != f for f, w in zip(t.shape, s.shape)):
                 wrong_shape.append(f"{n}: file has {list(t.shape)}, model wants {list(s.shape)}")
             if not t.dtype.is_floating_point:
                 wrong_type.append(f"{n} ({t.dtype})")

@@ -24,6 +24,8 @@ def random_tensors(expected: Dict[str, TensorSpec], seed: int, std: float, dtype
     out = {}
     for name in sorted(expected):
         spec = expected[name]
+        if any(n < 0 for n in spec.shape):      # sizes that only a checkpoint fixes: drawn at their stated default
+            spec = TensorSpec(tuple(abs(n) for n in spec.shape), spec.init, spec.optional, spec.lo, spec.hi)
         if spec.init == "ones":
             t = torch.ones(spec.shape, dtype=torch.float32)
         elif spec.init == "ones_jitter":
@@ -52,6 +54,8 @@ def random_tensors_on_device(expected: Dict[str, TensorSpec], seed: int, std: fl
     out = {}
     for name in sorted(expected):
         spec = expected[name]
+        if any(n < 0 for n in spec.shape):      # sizes that only a checkpoint fixes: drawn at their stated default
+            spec = TensorSpec(tuple(abs(n) for n in spec.shape), spec.init, spec.optional, spec.lo, spec.hi)
         if spec.init == "ones":
             t = torch.ones(spec.shape, dtype=torch.float32, device=device)
         elif spec.init == "ones_jitter":

@@ -290,3 +290,105 @@ class TorchOps:
         y = g @ w_proj.double().T
         s = s + y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps) * norm_w.double()
         residual.copy_(s.float())
+
+    # ------------------------------------------------------------------ operators of the Lilenex parts
+    def stream_mix_norm(self, streams, init, y, mix, out, read, weight, eps, n_streams, rows, dtype):
+        if streams is None:
+            streams = init.float()[:, None, :].repeat(1, n_streams, 1).contiguous()
+        new = streams.double()
+        if y is not None:
+            new = torch.einsum("st,nsw->ntw", mix.double(), new) + out.double()[None, :, None] * y.double()[:, None, :]
+        if rows is None:
+            streams.copy_(new.float())
+        else:
+            new = new[rows.long()]
+        u = torch.einsum("s,nsw->nw", read.double(), new)
+        normed = u / torch.sqrt((u * u).mean(-1, keepdim=True) + eps) * weight.double()
+        return normed.to(dtype), streams
+
+    def qk_norm_rotate_store(self, proj, H, G, d, dv, q_norm, k_norm, eps, positions, freq, dims, amplitude, slots, cache, page_size):
+        T = proj.shape[0]
+        x = proj.double()
+        q, k = x[:, :H * d], x[:, H * d:(H + G) * d]
+        if eps > 0:
+            q = q / torch.sqrt((q * q).mean(-1, keepdim=True) + eps) * q_norm.double()
+            if G:
+                k = k / torch.sqrt((k * k).mean(-1, keepdim=True) + eps) * k_norm.double()
+        qk = torch.cat([q, k], dim=1).view(T, H + G, d).clone()
+        if freq is not None and dims > 0:
+            ang = positions.double()[:, None] * freq.double()[None, :dims // 2]
+            c, s = (ang.cos() * amplitude)[:, None, :], (ang.sin() * amplitude)[:, None, :]
+            a, b = qk[..., 0:dims:2].clone(), qk[..., 1:dims:2].clone()
+            qk[..., 0:dims:2] = a * c - b * s
+            qk[..., 1:dims:2] = b * c + a * s
+        proj[:, :(H + G) * d] = qk.reshape(T, -1).to(proj.dtype)
+        if G and cache is not None:
+            for t in range(T):
+                sl = int(slots[t])
+                if sl < 0:
+                    continue
+                page, off = divmod(sl, page_size)
+                kp, vp = self._page_views(cache, page, G, page_size, d, dv)
+                kp[:, off] = proj[t, H * d:(H + G) * d].view(G, d)
+                vp[:, off] = proj[t, (H + G) * d:(H + G) * d + G * dv].view(G, dv)
+
+    def window_attention(self, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window=0, keep_first=0,
+                         splits=1, hints=None):
+        T = q.shape[0]
+        out = torch.zeros((T, H * dv), dtype=torch.float64)
+        group = H // G
+        for t in range(T):
+            r, p = int(tok_req[t]), int(positions[t])
+            if r < 0:
+                continue
+            keys = [j for j in range(p + 1) if not window or p - j < window or j < keep_first]
+            ks, vs = [], []
+            for j in keys:
+                page = int(block_table[r, j // page_size])
+                assert page >= 0, "attention reads a page that was given back"
+                kp, vp = self._page_views(cache, page, G, page_size, d, dv)
+                ks.append(kp[:, j % page_size].double())
+                vs.append(vp[:, j % page_size].double())
+            k, v = torch.stack(ks), torch.stack(vs)
+            qt = q[t, :H * d].double().view(H, d)
+            for h in range(H):
+                w = torch.softmax((k[:, h // group] @ qt[h]) * scale, 0)
+                out[t, h * dv:(h + 1) * dv] = w @ v[:, h // group]
+        return out.to(q.dtype)
+
+    def gla_scan(self, proj, z, bias, inv_tau, S_all, ctx, H, d, dv, q_scale):
+        T = proj.shape[0]
+        x = proj.double()
+        q = x[:, :H * d].view(T, H, d) * q_scale
+        k = x[:, H * d:2 * H * d].view(T, H, d)
+        v = x[:, 2 * H * d:2 * H * d + H * dv].view(T, H, dv)
+        decay = torch.exp(torch.nn.functional.logsigmoid(z.double() + bias.double()) * inv_tau).view(T, H, d)
+        o = torch.zeros((T, H, dv), dtype=torch.float64)
+        for lo, hi, slot, pos0 in self._requests(ctx):
+            S = S_all[slot].double() if pos0 > 0 else torch.zeros((H, d, dv), dtype=torch.float64)
+            for t in range(lo, hi):
+                S = decay[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+                o[t] = torch.einsum("hde,hd->he", S, q[t])
+            S_all[slot] = S.float()
+        return o.reshape(T, H * dv).float()
+
+    def gelu_tanh(self, x):
+        z = x.double()
+        return (0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))).to(x.dtype)
+
+    def routed_experts(self, x, logits, w_gate_up, w_down, top, scale_input, shared):
+        T = x.shape[0]
+        inter = w_gate_up.shape[1] // 2
+        score = torch.sigmoid(logits.double())
+        out = torch.zeros((T, w_down.shape[1]), dtype=torch.float64)
+        for t in range(T):
+            for e in score[t].topk(top).indices.tolist():
+                w = score[t, e]
+                u = (x[t].double() * w).to(x.dtype).double() if scale_input else x[t].double()
+                gu = w_gate_up[e].double() @ u
+                g, up = gu[:inter], gu[inter:]
+                y = w_down[e].double() @ (g * torch.sigmoid(g) * up)
+                out[t] += y if scale_input else w * y
+        if shared is not None:
+            out += shared.double()
+        return out.float()
