@@ -1,0 +1,131 @@
+// Gated linear attention: per head a float32 state S [d, dv] that decays per key channel,
+//   S <- diag(a_t) S + k_t v_t^T,   o_t = S^T q_t,   a_t = sigmoid(z_t + b)^(1/tau) = exp(logsigmoid(z_t + b) / tau).
+//
+// proj is the projection's output [T, q | k | v | ...] (H heads of d, d, dv), z float32 [T, H*d] before
+// the bias.  A block owns 32 columns of one head's state for one request and walks the request's
+// tokens of this step in order; 8 lanes share a column, each with every eighth packet of four of the d rows
+// in registers.  Tokens come through shared memory in batches (q scaled, decay worked out while
+// staging).  The state of a request is read from its slot unless the portion starts at position 0
+// and written back at the end.  Everything after the loads is float32; a token's result does not
+// depend on how the request was cut into steps or on what else the step holds.
+#include "common.cuh"
+
+namespace ptl {
+
+constexpr int kGlaCols = 32;      // columns of the state per block
+constexpr int kGlaLanes = 8;      // lanes per column
+constexpr int kGlaThreads = kGlaCols * kGlaLanes;
+
+__device__ __forceinline__ float log_sigmoid_f32(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
+
+template <typename T, int RPL, int TB>   // RPL rows per lane (d <= 8 * RPL), TB tokens per batch
+__global__ void __launch_bounds__(kGlaThreads)
+gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, const float* __restrict__ z,
+                const float* __restrict__ bias, float inv_tau, float* __restrict__ state, const int* __restrict__ q_start,
+                const int* __restrict__ positions, const int* __restrict__ state_slot, int H, int d, int dv, float q_scale) {
+  constexpr int DP = kGlaLanes * RPL;
+  __shared__ __align__(16) float s_q[TB][DP], s_k[TB][DP], s_a[TB][DP];
+  __shared__ float s_v[TB][kGlaCols];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int r = blockIdx.z, h = blockIdx.y;
+  const int t0 = q_start[r], t1 = q_start[r + 1];
+  const int slot = state_slot[r];
+  if (t1 <= t0 || slot < 0) return;
+  const int tid = threadIdx.x;
+  const int col = tid / kGlaLanes, lane8 = tid % kGlaLanes;
+  const int e = blockIdx.x * kGlaCols + col;
+  const bool live = e < dv;
+  // rows of this lane: packets of four, packet m of the lane being packet m * 8 + lane8 of the column, so that
+  // the eight lanes of a column read 128 consecutive bytes of a staged token
+  auto row_of = [&](int i) { return ((i >> 2) * kGlaLanes + lane8) * 4 + (i & 3); };
+  float* st = state + (((size_t)slot * H + h) * d) * dv;
+  float S[RPL];
+  const bool fresh = positions[t0] == 0;
+#pragma unroll
+  for (int i = 0; i < RPL; ++i) S[i] = (!fresh && live && row_of(i) < d) ? st[(size_t)row_of(i) * dv + e] : 0.f;
+  const int qcol = h * d, kcol = H * d + h * d, vcol = 2 * H * d + h * dv + blockIdx.x * kGlaCols;
+  const int vcols = min(kGlaCols, dv - blockIdx.x * kGlaCols);
+
+  for (int tb = t0; tb < t1; tb += TB) {
+    const int nt = min(TB, t1 - tb);
+    __syncthreads();
+    for (int idx = tid; idx < nt * DP; idx += kGlaThreads) {
+      const int j = idx / DP, c = idx % DP;
+      float qv = 0.f, kv = 0.f, av = 0.f;
+      if (c < d) {
+        const T* row = proj + (size_t)(tb + j) * ld;
+        qv = to_f32(row[qcol + c]) * q_scale;
+        kv = to_f32(row[kcol + c]);
+        av = expf(log_sigmoid_f32(z[(size_t)(tb + j) * H * d + qcol + c] + bias[qcol + c]) * inv_tau);
+      }
+      s_q[j][c] = qv;
+      s_k[j][c] = kv;
+      s_a[j][c] = av;
+    }
+    for (int idx = tid; idx < nt * kGlaCols; idx += kGlaThreads) {
+      const int j = idx / kGlaCols, c = idx % kGlaCols;
+      s_v[j][c] = c < vcols ? to_f32(proj[(size_t)(tb + j) * ld + vcol + c]) : 0.f;
+    }
+    __syncthreads();
+    for (int j = 0; j < nt; ++j) {
+      const float v = s_v[j][col];
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < RPL; i += 4) {
+        const float4 a4 = *reinterpret_cast<const float4*>(&s_a[j][row_of(i)]);
+        const float4 k4 = *reinterpret_cast<const float4*>(&s_k[j][row_of(i)]);
+        const float4 q4 = *reinterpret_cast<const float4*>(&s_q[j][row_of(i)]);
+        S[i] = fmaf(a4.x, S[i], k4.x * v);
+        S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * v);
+        S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * v);
+        S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * v);
+        acc = fmaf(q4.x, S[i], acc);
+        acc = fmaf(q4.y, S[i + 1], acc);
+        acc = fmaf(q4.z, S[i + 2], acc);
+        acc = fmaf(q4.w, S[i + 3], acc);
+      }
+      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
+      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
+      if (lane8 == 0 && live) out[(size_t)(tb + j) * H * dv + (size_t)h * dv + e] = acc;
+    }
+  }
+  if (live) {
+#pragma unroll
+    for (int i = 0; i < RPL; ++i)
+      if (row_of(i) < d) st[(size_t)row_of(i) * dv + e] = S[i];
+  }
+}
+
+template <typename T>
+int gla_scan(float* out, const void* proj, int ld, const float* z, const float* bias, float inv_tau, float* state,
+             const int* q_start, const int* positions, const int* state_slot, int requests, int H, int d, int dv,
+             float q_scale, void* stream) {
+  PTL_REQUIRE(requests >= 0 && H > 0 && d > 0 && dv > 0, "gla_scan: bad sizes");
+  PTL_REQUIRE(d <= 256, "gla_scan: head size %d, at most 256", d);
+  PTL_REQUIRE(ld >= 2 * H * d + H * dv, "gla_scan: rows of %d elements are too short", ld);
+  PTL_REQUIRE(H <= 65535 && requests <= 65535, "gla_scan: too many heads or requests");
+  if (requests == 0) return 0;
+  const dim3 grid((dv + kGlaCols - 1) / kGlaCols, H, requests), block(kGlaThreads);
+#define PTL_GLA_LAUNCH(RPL, TB)                                                                                              \
+  return launch_kernel("gla_scan", gla_scan_kernel<T, RPL, TB>, grid, block, 0, as_stream(stream), out, (const T*)proj, ld, z, \
+                       bias, inv_tau, state, q_start, positions, state_slot, H, d, dv, q_scale)
+  if (d <= 32) PTL_GLA_LAUNCH(4, 16);
+  if (d <= 64) PTL_GLA_LAUNCH(8, 16);
+  if (d <= 128) PTL_GLA_LAUNCH(16, 16);
+  PTL_GLA_LAUNCH(32, 8);
+#undef PTL_GLA_LAUNCH
+}
+
+}  // namespace ptl
+
+#define PTL_GLA(SUFFIX, TYPE)                                                                                                   \
+  PTL_EXPORT int ptl_gla_scan##SUFFIX(float* out, const void* proj, int ld, const float* z, const float* bias, float inv_tau,    \
+                                      float* state, const int* q_start, const int* positions, const int* state_slot,            \
+                                      int requests, int H, int d, int dv, float q_scale, void* stream) {                        \
+    return ptl::gla_scan<TYPE>(out, proj, ld, z, bias, inv_tau, state, q_start, positions, state_slot, requests, H, d, dv,       \
+                               q_scale, stream);                                                                                \
+  }
+PTL_GLA(_f32, float)
+PTL_GLA(_bf16, __nv_bfloat16)

@@ -1,0 +1,447 @@
+// Routed mixture of experts without a word coming back to the host: route, sort by expert on the
+// device, grouped products over tiles of tokens of one expert each, combine.
+//
+//   moe_route     one warp per token: score = sigmoid(logit) in float32, the `top` largest scores (the
+//                 lower index wins a tie), expert ids and scores out.
+//   moe_plan      one block: tokens per expert, each expert's rows padded to whole tiles of kMoeTile rows,
+//                 the list of tiles (expert, first row, rows), the row of every (token, choice).
+//   moe_gather    sorted[row] = x[token] (* score when the weight multiplies the expert's input), rounded to T.
+//   moe_grouped   C[row, :] = A[row, :] . W[expert]^T for the rows of a tile; either plain (float32 out) or
+//                 with W = [gate rows | up rows] and silu(gate) * up as the result (T out).  CUDA-core
+//                 form for both element types: sums run over K in ascending order in chunks of 32 that are
+//                 added to the total one by one, the same for every row wherever it lies in its tile.
+//   moe_combine   out[token] = shared[token] + sum over its choices of C[row] (times the score when the
+//                 weight multiplies the expert's output), float32.
+// A block that finds its tile index beyond the tile count returns at once: the grid is sized for the
+// most tiles a step of this many tokens can have.
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+namespace ptl {
+
+constexpr int kMoeTile = 32;          // rows of a tile
+constexpr int kMoeMaxExperts = 1024;
+
+__device__ __forceinline__ float sigmoid_f32(float x) { return 1.0f / (1.0f + expf(-x)); }
+__device__ __forceinline__ float moe_silu(float x) { return x / (1.0f + expf(-x)); }
+
+// ------------------------------------------------------------------ route
+__global__ void __launch_bounds__(128)
+moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits, int tokens, int E,
+                 int top) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= tokens) return;
+  constexpr int kPerLane = kMoeMaxExperts / 32;
+  float sc[kPerLane];
+#pragma unroll
+  for (int i = 0; i < kPerLane; ++i) {
+    const int e = lane + 32 * i;
+    float v = -INFINITY;
+    if (e < E) {
+      v = sigmoid_f32(logits[(size_t)t * E + e]);
+      if (!(v == v)) v = -INFINITY;        // a NaN never wins
+    }
+    sc[i] = v;
+  }
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i) {
+      const int e = lane + 32 * i;
+      if (e < E && sc[i] > best) { best = sc[i]; best_e = e; }     // ascending e: the lower index stays on a tie
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (ob > best || (ob == best && oe < best_e)) { best = ob; best_e = oe; }
+    }
+    if (best_e >= E) { best_e = k % E; best = 0.f; }            // nothing finite left: a valid expert with weight 0
+    if (lane == 0) { ids[(size_t)t * top + k] = best_e; weights[(size_t)t * top + k] = best; }
+#pragma unroll
+    for (int i = 0; i < kPerLane; ++i)
+      if (lane + 32 * i == best_e) sc[i] = -INFINITY;
+  }
+}
+
+// ------------------------------------------------------------------ plan
+// tiles: [max_tiles][3] = expert, first row, rows; meta[0] = number of tiles.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(int* __restrict__ pos, int* __restrict__ tiles, int* __restrict__ meta, const int* __restrict__ ids, int n,
+                int E, int max_tiles) {
+  __shared__ int cnt[kMoeMaxExperts], first[kMoeMaxExperts], tile0[kMoeMaxExperts];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tid = threadIdx.x;
+  for (int e = tid; e < E; e += blockDim.x) cnt[e] = 0;
+  __syncthreads();
+  for (int a = tid; a < n; a += blockDim.x) {
+    const int e = ids[a];
+    if (e >= 0 && e < E) atomicAdd(&cnt[e], 1);
+  }
+  __syncthreads();
+  if (tid < 32) {
+    // exclusive sums of the experts' tile counts, 32 experts at a time
+    int running = 0;
+    for (int e0 = 0; e0 < E; e0 += 32) {
+      const int e = e0 + tid;
+      const int nt = e < E ? (cnt[e] + kMoeTile - 1) / kMoeTile : 0;
+      int incl = nt;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int v = __shfl_up_sync(0xffffffffu, incl, o);
+        if (tid >= o) incl += v;
+      }
+      if (e < E) { tile0[e] = running + incl - nt; first[e] = (running + incl - nt) * kMoeTile; }
+      running += __shfl_sync(0xffffffffu, incl, 31);
+    }
+    if (tid == 0) meta[0] = min(running, max_tiles);
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) {
+    const int c = cnt[e];
+    for (int i = 0, r = 0; r < c; ++i, r += kMoeTile) {
+      const int ti = tile0[e] + i;
+      if (ti < max_tiles) {
+        tiles[3 * ti] = e;
+        tiles[3 * ti + 1] = first[e] + r;
+        tiles[3 * ti + 2] = min(kMoeTile, c - r);
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = tid; e < E; e += blockDim.x) cnt[e] = first[e];       // now the next free row of each expert
+  __syncthreads();
+  for (int a = tid; a < n; a += blockDim.x) {
+    const int e = ids[a];
+    pos[a] = (e >= 0 && e < E) ? atomicAdd(&cnt[e], 1) : -1;
+  }
+}
+
+// ------------------------------------------------------------------ gather
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_gather_kernel(T* __restrict__ sorted, const T* __restrict__ x, const int* __restrict__ pos, const float* __restrict__ weights,
+                  int top, int width, int scale_input) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int a = blockIdx.x;
+  const int row = pos[a];
+  if (row < 0) return;
+  const float w = scale_input ? weights[a] : 1.f;
+  const T* src = x + (size_t)(a / top) * width;
+  T* dst = sorted + (size_t)row * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = scale_input ? from_f32<T>(to_f32(src[i]) * w) : src[i];
+}
+
+// ------------------------------------------------------------------ grouped product on the CUDA cores
+// 256 threads: thread (tx, ty) owns rows 2*ty, 2*ty+1 and columns tx, tx+16, tx+32, tx+48 of a 32 x 64 tile.
+// GATED: tile columns 0..31 are gate rows j0.., columns 32..63 the up rows of the same features; the result has 32 columns.
+template <typename T, typename OUT, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_kernel(OUT* __restrict__ C, int ldc, const T* __restrict__ A, const T* __restrict__ W, const int* __restrict__ tiles,
+                   const int* __restrict__ meta, int N, int K, size_t expert_stride, int half) {
+  __shared__ float sa[kMoeTile][33], sb[64][33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tile = blockIdx.x;
+  if (tile >= meta[0]) return;
+  const int expert = tiles[3 * tile], row0 = tiles[3 * tile + 1], rows = tiles[3 * tile + 2];
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  const int j0 = blockIdx.y * (GATED ? 32 : 64);           // first output feature of the tile
+  const T* Wexp = W + (size_t)expert * expert_stride;
+  float total[2][4], chunk[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) total[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += 32) {
+    __syncthreads();
+    for (int idx = tid; idx < kMoeTile * 32; idx += 256) {
+      const int rr = idx >> 5, kk = idx & 31;
+      sa[rr][kk] = (rr < rows && k0 + kk < K) ? to_f32(A[(size_t)(row0 + rr) * K + k0 + kk]) : 0.f;
+    }
+    for (int idx = tid; idx < 64 * 32; idx += 256) {
+      const int cc = idx >> 5, kk = idx & 31;
+      int wrow;
+      bool ok;
+      if (GATED) {
+        const int f = j0 + (cc & 31);
+        ok = f < half;
+        wrow = (cc < 32 ? 0 : half) + f;
+      } else {
+        wrow = j0 + cc;
+        ok = wrow < N;
+      }
+      sb[cc][kk] = (ok && k0 + kk < K) ? to_f32(Wexp[(size_t)wrow * K + k0 + kk]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) chunk[i][j] = 0.f;
+#pragma unroll
+    for (int kk = 0; kk < 32; ++kk) {
+      const float a0 = sa[2 * ty][kk], a1 = sa[2 * ty + 1][kk];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float b = sb[tx + 16 * j][kk];
+        chunk[0][j] = fmaf(a0, b, chunk[0][j]);
+        chunk[1][j] = fmaf(a1, b, chunk[1][j]);
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i)
+#pragma unroll
+      for (int j = 0; j < 4; ++j) total[i][j] += chunk[i][j];
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int rr = 2 * ty + i;
+    if (rr >= rows) continue;
+    OUT* dst = C + (size_t)(row0 + rr) * ldc;
+    if (GATED) {
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int f = j0 + tx + 16 * j;
+        if (f < half) dst[f] = from_f32<OUT>(moe_silu(total[i][j]) * total[i][j + 2]);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int c = j0 + tx + 16 * j;
+        if (c < N) dst[c] = from_f32<OUT>(total[i][j]);
+      }
+    }
+  }
+}
+
+// ------------------------------------------------------------------ grouped product on the tensor cores (bfloat16)
+// The same tiles with mma.sync m16n8k16: 4 warps, warp w owns columns 16*w .. 16*w+15 of the 32 x 64 tile (two
+// 16-row halves x two 8-column halves), operands staged through shared memory 32 values of K at a time with rows
+// padded to 40 elements so that the fragment loads of a warp fall into different banks.
+template <typename OUT, bool GATED>
+__global__ void __launch_bounds__(128)
+moe_grouped_mma_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                       const int* __restrict__ tiles, const int* __restrict__ meta, int N, int K, size_t expert_stride,
+                       int half) {
+  constexpr int kPitch = 40;
+  __shared__ __align__(16) __nv_bfloat16 sa[2][kMoeTile][kPitch], sb[2][64][kPitch];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tile = blockIdx.x;
+  if (tile >= meta[0]) return;
+  const int expert = tiles[3 * tile], row0 = tiles[3 * tile + 1], rows = tiles[3 * tile + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, c = lane & 3;
+  const int j0 = blockIdx.y * (GATED ? 32 : 64);
+  const __nv_bfloat16* Wexp = W + (size_t)expert * expert_stride;
+  // GATED: warp w < 2 holds gate features j0 + 16*w .., warp w >= 2 the up rows of features j0 + 16*(w-2) ..; the
+  // epilogue pairs them through shared memory
+  float acc[2][2][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
+
+  auto stage = [&](int k0, int buf) {
+    // 32 rows x 32 k of A: 128 packets of 8; 64 rows x 32 k of W: 256 packets
+    {
+      const int rr = tid >> 2, ch = tid & 3;
+      const bool ok = rr < rows;
+      cp_async_16(smem_u32(&sa[buf][rr][ch * 8]), A + (size_t)(row0 + (ok ? rr : 0)) * K + k0 + ch * 8, ok);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      const int idx = tid + 128 * i;
+      const int cc = idx >> 2, ch = idx & 3;
+      int wrow;
+      bool ok;
+      if (GATED) {
+        const int f = j0 + (cc & 31);
+        ok = f < half;
+        wrow = (cc < 32 ? 0 : half) + f;
+      } else {
+        wrow = j0 + cc;
+        ok = wrow < N;
+      }
+      cp_async_16(smem_u32(&sb[buf][cc][ch * 8]), Wexp + (size_t)(ok ? wrow : 0) * K + k0 + ch * 8, ok);
+    }
+  };
+  const int nk = K / 32;
+  stage(0, 0);
+  cp_async_commit();
+  for (int kb = 0; kb < nk; ++kb) {
+    if (kb + 1 < nk) stage((kb + 1) * 32, (kb + 1) & 1);
+    cp_async_commit();
+    cp_async_wait<1>();
+    __syncthreads();
+    const int buf = kb & 1;
+#pragma unroll
+    for (int ks = 0; ks < 2; ++ks) {
+      uint32_t bfrag[2][2];
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt) {
+        const __nv_bfloat16* bp = &sb[buf][warp * 16 + nt * 8 + g][ks * 16 + 2 * c];
+        bfrag[nt][0] = *reinterpret_cast<const uint32_t*>(bp);
+        bfrag[nt][1] = *reinterpret_cast<const uint32_t*>(bp + 8);
+      }
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        uint32_t afrag[4];
+        const __nv_bfloat16* ap = &sa[buf][mt * 16 + g][ks * 16 + 2 * c];
+        afrag[0] = *reinterpret_cast<const uint32_t*>(ap);
+        afrag[1] = *reinterpret_cast<const uint32_t*>(ap + 8 * kPitch);
+        afrag[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
+        afrag[3] = *reinterpret_cast<const uint32_t*>(ap + 8 * kPitch + 8);
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) mma_bf16_16816(acc[mt][nt], afrag, bfrag[nt][0], bfrag[nt][1]);
+      }
+    }
+    __syncthreads();
+  }
+  cp_async_wait<0>();
+  if (GATED) {
+    // up values go through shared memory to the warp that holds the gates of the same features
+    __shared__ float s_up[kMoeTile][33];
+    if (warp >= 2) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e)
+            s_up[mt * 16 + g + (e >> 1) * 8][(warp - 2) * 16 + nt * 8 + 2 * c + (e & 1)] = acc[mt][nt][e];
+    }
+    __syncthreads();
+    if (warp < 2) {
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int rr = mt * 16 + g + (e >> 1) * 8, cc = warp * 16 + nt * 8 + 2 * c + (e & 1);
+            const int f = j0 + cc;
+            if (rr < rows && f < half) C[(size_t)(row0 + rr) * ldc + f] = from_f32<OUT>(moe_silu(acc[mt][nt][e]) * s_up[rr][cc]);
+          }
+    }
+  } else {
+#pragma unroll
+    for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+      for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int rr = mt * 16 + g + (e >> 1) * 8, cc = j0 + warp * 16 + nt * 8 + 2 * c + (e & 1);
+          if (rr < rows && cc < N) C[(size_t)(row0 + rr) * ldc + cc] = from_f32<OUT>(acc[mt][nt][e]);
+        }
+  }
+}
+
+// ------------------------------------------------------------------ combine
+template <typename T>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(float* __restrict__ out, const float* __restrict__ C, const T* __restrict__ shared_out,
+                   const int* __restrict__ pos, const float* __restrict__ weights, int top, int width, int scale_input) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float acc = shared_out ? to_f32(shared_out[(size_t)t * width + i]) : 0.f;
+    for (int k = 0; k < top; ++k) {
+      const int row = pos[(size_t)t * top + k];
+      if (row < 0) continue;
+      const float v = C[(size_t)row * width + i];
+      acc = scale_input ? acc + v : fmaf(weights[(size_t)t * top + k], v, acc);
+    }
+    out[(size_t)t * width + i] = acc;
+  }
+}
+
+// ------------------------------------------------------------------ launchers
+int moe_route(int* ids, float* weights, const float* logits, int tokens, int E, int top, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && E >= 1 && E <= kMoeMaxExperts && top >= 1 && top <= E, "moe_route: %d experts, top %d (at most %d experts)", E, top, kMoeMaxExperts);
+  if (tokens == 0) return 0;
+  return launch_kernel("moe_route", moe_route_kernel, dim3((tokens + 3) / 4), dim3(128), 0, as_stream(stream), ids, weights, logits,
+                       tokens, E, top);
+}
+
+int moe_plan(int* pos, int* tiles, int* meta, const int* ids, int n, int E, int max_tiles, void* stream) {
+  PTL_REQUIRE(n >= 0 && E >= 1 && E <= kMoeMaxExperts && max_tiles >= (n + kMoeTile - 1) / kMoeTile, "moe_plan: bad sizes");
+  return launch_kernel("moe_plan", moe_plan_kernel, dim3(1), dim3(1024), 0, as_stream(stream), pos, tiles, meta, ids, n, E, max_tiles);
+}
+
+template <typename T>
+int moe_gather(void* sorted, const void* x, const int* pos, const float* weights, int n, int top, int width, int scale_input,
+               void* stream) {
+  PTL_REQUIRE(n >= 0 && top >= 1 && width > 0, "moe_gather: bad sizes");
+  if (n == 0) return 0;
+  return launch_kernel("moe_gather", moe_gather_kernel<T>, dim3(n), dim3(128), 0, as_stream(stream), (T*)sorted, (const T*)x, pos,
+                       weights, top, width, scale_input);
+}
+
+template <typename T>
+int moe_grouped(void* C, int ldc, const void* A, const void* W, const int* tiles, const int* meta, int max_tiles, int N, int K,
+                int gated, int tensor_cores, void* stream) {
+  PTL_REQUIRE(max_tiles >= 0 && N > 0 && K > 0 && (!gated || N % 2 == 0), "moe_grouped: bad sizes N=%d K=%d", N, K);
+  if (max_tiles == 0) return 0;
+  const int half = N / 2;
+  const size_t stride = (size_t)N * K;
+  const dim3 grid(max_tiles, gated ? (half + 31) / 32 : (N + 63) / 64);
+  PTL_REQUIRE(grid.y <= 65535, "moe_grouped: too many column tiles");
+  if constexpr (sizeof(T) == 2) {
+    if (tensor_cores && K % 32 == 0 && aligned16(A) && aligned16(W)) {
+      if (gated)
+        return launch_kernel("moe_grouped_mma", moe_grouped_mma_kernel<T, true>, grid, dim3(128), 0, as_stream(stream), (T*)C, ldc,
+                             (const T*)A, (const T*)W, tiles, meta, N, K, stride, half);
+      return launch_kernel("moe_grouped_mma", moe_grouped_mma_kernel<float, false>, grid, dim3(128), 0, as_stream(stream), (float*)C,
+                           ldc, (const T*)A, (const T*)W, tiles, meta, N, K, stride, half);
+    }
+  }
+  if (gated)
+    return launch_kernel("moe_grouped", moe_grouped_kernel<T, T, true>, grid, dim3(256), 0, as_stream(stream), (T*)C, ldc, (const T*)A,
+                         (const T*)W, tiles, meta, N, K, stride, half);
+  return launch_kernel("moe_grouped", moe_grouped_kernel<T, float, false>, grid, dim3(256), 0, as_stream(stream), (float*)C, ldc,
+                       (const T*)A, (const T*)W, tiles, meta, N, K, stride, half);
+}
+
+template <typename T>
+int moe_combine(float* out, const float* C, const void* shared_out, const int* pos, const float* weights, int tokens, int top,
+                int width, int scale_input, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && top >= 1 && width > 0, "moe_combine: bad sizes");
+  if (tokens == 0) return 0;
+  return launch_kernel("moe_combine", moe_combine_kernel<T>, dim3(tokens), dim3(256), 0, as_stream(stream), out, C,
+                       (const T*)shared_out, pos, weights, top, width, scale_input);
+}
+
+}  // namespace ptl
+
+PTL_EXPORT int ptl_moe_tile_rows() { return ptl::kMoeTile; }
+PTL_EXPORT int ptl_moe_route(int* ids, float* weights, const float* logits, int tokens, int E, int top, void* stream) {
+  return ptl::moe_route(ids, weights, logits, tokens, E, top, stream);
+}
+PTL_EXPORT int ptl_moe_plan(int* pos, int* tiles, int* meta, const int* ids, int n, int E, int max_tiles, void* stream) {
+  return ptl::moe_plan(pos, tiles, meta, ids, n, E, max_tiles, stream);
+}
+#define PTL_MOE(SUFFIX, TYPE)                                                                                                     \
+  PTL_EXPORT int ptl_moe_gather##SUFFIX(void* sorted, const void* x, const int* pos, const float* weights, int n, int top,         \
+                                        int width, int scale_input, void* stream) {                                               \
+    return ptl::moe_gather<TYPE>(sorted, x, pos, weights, n, top, width, scale_input, stream);                                    \
+  }                                                                                                                               \
+  PTL_EXPORT int ptl_moe_grouped##SUFFIX(void* C, int ldc, const void* A, const void* W, const int* tiles, const int* meta,        \
+                                         int max_tiles, int N, int K, int gated, int tensor_cores, void* stream) {                \
+    return ptl::moe_grouped<TYPE>(C, ldc, A, W, tiles, meta, max_tiles, N, K, gated, tensor_cores, stream);                       \
+  }                                                                                                                               \
+  PTL_EXPORT int ptl_moe_combine##SUFFIX(float* out, const float* C, const void* shared_out, const int* pos,                       \
+                                         const float* weights, int tokens, int top, int width, int scale_input, void* stream) {   \
+    return ptl::moe_combine<TYPE>(out, C, shared_out, pos, weights, tokens, top, width, scale_input, stream);                     \
+  }
+PTL_MOE(_f32, float)
+PTL_MOE(_bf16, __nv_bfloat16)

@@ -1,0 +1,349 @@
+// Softmax attention behind a sliding window that keeps the first positions, over the paged cache,
+// and the kernel that prepares its inputs.
+//
+// A page of the cache holds its keys, then its values: key n of kv head g lies at
+//   page * G * page_size * (d + dv) + (g * page_size + n % page_size) * d,
+// its value at  page * G * page_size * (d + dv) + G * page_size * d + (g * page_size + n % page_size) * dv.
+// (With dv == d this is the [pages][2][G][page_size][d] layout of the other attention kernels.)
+//
+// qk_norm_rotate_store, per token of the step, on the projection's output [T, q | k | v]:
+//   q <- q * rsqrt(mean(q^2) + eps) * wq   over ALL heads of the token at once; k likewise     (eps > 0)
+//   pairs (2i, 2i+1), i < dims/2, of every q and k head are turned by the angle float(position) * freq[i],
+//   cos and sin multiplied by `amplitude`;
+//   q and k are written back in place (rounded once), k and v go to the token's slot of the cache.
+//
+// window_attention: token t (request r, position p) sees key j <= p if p - j < window or j < keep
+// (window 0: every j <= p).  One warp per (token, query head); the visible keys are walked as one
+// list (the kept ones that the window has passed, then the window), 32 at a time, one key per
+// lane; scores, softmax and the weighted sum of values are float32, with float32 inputs compensated
+// (see attention_simt.cu).  The list may be split over blockIdx.z and merged by a second kernel.
+#include "common.cuh"
+
+namespace ptl {
+
+// ------------------------------------------------------------------ norm + rotation + cache write
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_rotate_store_kernel(T* __restrict__ proj, int ld, int H, int G, int d, int dv, const float* __restrict__ wq,
+                            const float* __restrict__ wk, float eps, const int* __restrict__ positions,
+                            const float* __restrict__ freq, int dims, float amplitude, const int* __restrict__ slots,
+                            T* __restrict__ cache, int page_size, long long num_slots) {
+  __shared__ float red[33];
+  pdl_wait();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  T* row = proj + (size_t)t * ld;
+  const int nq = H * d, nk = G * d, nv = G * dv;
+  float rq = 1.f, rk = 1.f;
+  if (eps > 0.f) {
+    float sq = 0.f, sk = 0.f;
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = to_f32(row[i]); sq = fmaf(v, v, sq); }
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) { const float v = to_f32(row[nq + i]); sk = fmaf(v, v, sk); }
+    sq = block_sum(sq, red);
+    rq = 1.0f / sqrtf(sq / (float)nq + eps);
+    if (nk > 0) {
+      sk = block_sum(sk, red);
+      rk = 1.0f / sqrtf(sk / (float)nk + eps);
+    }
+  }
+  const float pos = (float)positions[t];
+  long long slot = (slots && cache) ? (long long)slots[t] : -1;
+  if (slot >= num_slots) slot = -1;
+  const size_t page_stride = (size_t)G * page_size * (d + dv);
+  T* kdst = nullptr;
+  T* vdst = nullptr;
+  if (slot >= 0) {
+    const size_t page = (size_t)(slot / page_size), off = (size_t)(slot % page_size);
+    kdst = cache + page * page_stride + off * d;                                  // + g * page_size * d
+    vdst = cache + page * page_stride + (size_t)G * page_size * d + off * dv;     // + g * page_size * dv
+  }
+  // q and k, two neighbours per thread and turn (d is even when anything is rotated; an odd last entry is handled alone)
+  const int heads = H + G;
+  const int pairs_per_head = (d + 1) / 2;
+  for (int idx = threadIdx.x; idx < heads * pairs_per_head; idx += blockDim.x) {
+    const int h = idx / pairs_per_head, i = idx % pairs_per_head;
+    const int e0 = 2 * i, e1 = 2 * i + 1;
+    const bool is_k = h >= H;
+    const float r = is_k ? rk : rq;
+    const float* w = eps > 0.f ? (is_k ? wk + (size_t)(h - H) * d : wq + (size_t)h * d) : nullptr;
+    T* src = row + (size_t)h * d;
+    float a = to_f32(src[e0]) * r * (w ? w[e0] : 1.f);
+    float b = e1 < d ? to_f32(src[e1]) * r * (w ? w[e1] : 1.f) : 0.f;
+    if (freq && e1 < dims) {
+      float sn, cs;
+      sincosf(pos * freq[i], &sn, &cs);
+      float o1, o2;
+      rope_rotate(a, b, cs * amplitude, sn * amplitude, o1, o2);
+      a = o1;
+      b = o2;
+    }
+    const T ta = from_f32<T>(a), tb = from_f32<T>(b);
+    src[e0] = ta;
+    if (e1 < d) src[e1] = tb;
+    if (is_k && kdst) {
+      T* kd = kdst + (size_t)(h - H) * page_size * d;
+      kd[e0] = ta;
+      if (e1 < d) kd[e1] = tb;
+    }
+  }
+  if (vdst) {
+    const T* v = row + nq + nk;
+    for (int i = threadIdx.x; i < nv; i += blockDim.x) {
+      const int g = i / dv, e = i % dv;
+      vdst[(size_t)g * page_size * dv + e] = v[i];
+    }
+  }
+}
+
+template <typename T>
+int qk_norm_rotate_store(void* proj, int tokens, int ld, int H, int G, int d, int dv, const float* wq, const float* wk, float eps,
+                         const int* positions, const float* freq, int dims, float amplitude, const int* slots, void* cache,
+                         int page_size, long long num_slots, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && H > 0 && G >= 0 && d > 0 && dv > 0 && page_size > 0, "qk_norm_rotate_store: bad sizes");
+  PTL_REQUIRE(ld >= H * d + G * (d + dv), "qk_norm_rotate_store: rows of %d elements are too short", ld);
+  PTL_REQUIRE(eps <= 0.f || (wq && (G == 0 || wk)), "qk_norm_rotate_store: the norm needs its weights");
+  PTL_REQUIRE(dims >= 0 && dims % 2 == 0 && dims <= d && (dims == 0 || freq), "qk_norm_rotate_store: rotary width %d of head size %d", dims, d);
+  if (tokens == 0) return 0;
+  return launch_kernel("qk_norm_rotate_store", qk_norm_rotate_store_kernel<T>, dim3(tokens), dim3(256), 0, as_stream(stream),
+                       (T*)proj, ld, H, G, d, dv, wq, wk, eps, positions, dims > 0 ? freq : nullptr, dims, amplitude,
+                       G > 0 ? slots : nullptr, (T*)cache, page_size, num_slots);
+}
+
+// ------------------------------------------------------------------ attention
+constexpr int kWaMaxPerLane = 8;   // value heads up to 256
+constexpr int kWaWarps = 4;
+
+__device__ __forceinline__ void wa_two_fma(float& hi, float& lo, float a, float b) {
+  const float h = __fmul_rn(a, b);
+  const float r = fmaf(a, b, -h);
+  const float t = __fadd_rn(hi, h);
+  const float z = __fsub_rn(t, hi);
+  const float e = __fadd_rn(__fsub_rn(hi, __fsub_rn(t, z)), __fsub_rn(h, z));
+  hi = t;
+  lo = __fadd_rn(lo, __fadd_rn(e, r));
+}
+__device__ __forceinline__ void wa_two_scale(float& hi, float& lo, float c) {
+  const float h = __fmul_rn(hi, c);
+  lo = fmaf(lo, c, fmaf(hi, c, -h));
+  hi = h;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(kWaWarps * 32)
+window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float* __restrict__ part_ml,
+                        const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
+                        const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride, int out_stride,
+                        int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep,
+                        int splits, int num_pages, int vec_ok) {
+  extern __shared__ float qs_all[];  // [warps][d]
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t = blockIdx.x;
+  const int h = blockIdx.y * kWaWarps + warp;
+  if (h >= H) return;
+  const int split = blockIdx.z;
+  float* qs = qs_all + warp * d;
+  const T* qrow = q + (size_t)t * q_stride + (size_t)h * d;
+  constexpr bool kCompensated = sizeof(T) == 4;
+  for (int i = lane; i < d; i += 32) qs[i] = kCompensated ? to_f32(qrow[i]) : to_f32(qrow[i]) * scale;
+  __syncwarp();
+
+  const int r = tok_req[t];        // r < 0: a padding row; it sees no key and yields zeros
+  const int p = positions[t];
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int n_keep = min(keep, lo);                 // kept positions that the window has passed
+  const int n_list = r < 0 ? 0 : n_keep + (p - lo + 1);
+  int chunk = (n_list + splits - 1) / splits;
+  chunk = (chunk + 31) & ~31;
+  const int i_begin = split * chunk;
+  const int i_end = min(i_begin + chunk, n_list);
+  const int g = h / (H / G);
+  const size_t page_stride = (size_t)G * page_size * (d + dv);
+  const size_t v_plane = (size_t)G * page_size * d;
+  const int* bt = block_table + (size_t)(r < 0 ? 0 : r) * bt_stride;
+  constexpr int VN = Vec16<T>::N;
+
+  float m = -INFINITY, l = 0.f, l_lo = 0.f;
+  float acc[kWaMaxPerLane], acc_lo[kWaMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kWaMaxPerLane; ++i) { acc[i] = 0.f; acc_lo[i] = 0.f; }
+
+  for (int i0 = i_begin; i0 < i_end; i0 += 32) {
+    const int li = i0 + lane;
+    bool valid = li < i_end;
+    const int key = li < n_keep ? li : lo + (li - n_keep);
+    size_t vbase = 0;
+    float s = -INFINITY;
+    const int page = valid ? bt[key / page_size] : 0;
+    if (page < 0 || page >= num_pages) valid = false;   // never follow a table entry outside the pool
+    if (valid) {
+      const size_t in_page = (size_t)g * page_size + key % page_size;
+      const T* kp = cache + (size_t)page * page_stride + in_page * d;
+      vbase = (size_t)page * page_stride + v_plane + in_page * dv;
+      float dot = 0.f, dot_lo = 0.f;
+      if (vec_ok) {
+        for (int i = 0; i < d; i += VN) {
+          Vec16<T> kv = load16(kp + i);
+#pragma unroll
+          for (int e = 0; e < VN; ++e) {
+            if constexpr (kCompensated) wa_two_fma(dot, dot_lo, qs[i + e], kv.get(e));
+            else dot = fmaf(qs[i + e], kv.get(e), dot);
+          }
+        }
+      } else {
+        for (int i = 0; i < d; ++i) {
+          if constexpr (kCompensated) wa_two_fma(dot, dot_lo, qs[i], to_f32(kp[i]));
+          else dot = fmaf(qs[i], to_f32(kp[i]), dot);
+        }
+      }
+      s = kCompensated ? __fadd_rn(dot, dot_lo) * scale : dot;
+    }
+    const float m_new = fmaxf(m, warp_max(s));
+    const float pr = valid ? expf(s - m_new) : 0.f;
+    const float alpha = expf(m - m_new);
+    if constexpr (kCompensated) {
+      if (alpha != 1.f) {
+        wa_two_scale(l, l_lo, alpha);
+#pragma unroll
+        for (int i = 0; i < kWaMaxPerLane; ++i) wa_two_scale(acc[i], acc_lo[i], alpha);
+      }
+      wa_two_fma(l, l_lo, warp_sum(pr), 1.f);
+    } else {
+      l = l * alpha + warp_sum(pr);
+#pragma unroll
+      for (int i = 0; i < kWaMaxPerLane; ++i) acc[i] *= alpha;
+    }
+    m = m_new;
+    const int nvalid = min(32, i_end - i0);
+    for (int j = 0; j < nvalid; ++j) {
+      const float pj = __shfl_sync(0xffffffffu, pr, j);
+      const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)vbase, j);
+      if (pj == 0.f) continue;   // uniform over the warp: a skipped key has no valid address
+      const T* vp = cache + (size_t)bj;
+#pragma unroll
+      for (int i = 0; i < kWaMaxPerLane; ++i) {
+        const int dd = lane + 32 * i;
+        if (dd < dv) {
+          if constexpr (kCompensated) wa_two_fma(acc[i], acc_lo[i], pj, to_f32(vp[dd]));
+          else acc[i] = fmaf(pj, to_f32(vp[dd]), acc[i]);
+        }
+      }
+    }
+  }
+  if constexpr (kCompensated) {
+    l = __fadd_rn(l, l_lo);
+#pragma unroll
+    for (int i = 0; i < kWaMaxPerLane; ++i) acc[i] = __fadd_rn(acc[i], acc_lo[i]);
+  }
+  if (splits == 1) {
+    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    T* o = out + (size_t)t * out_stride + (size_t)h * dv;
+#pragma unroll
+    for (int i = 0; i < kWaMaxPerLane; ++i) {
+      const int dd = lane + 32 * i;
+      if (dd < dv) o[dd] = from_f32<T>(acc[i] * inv);
+    }
+  } else {
+    const size_t idx = ((size_t)t * H + h) * splits + split;
+    float* pa = part_acc + idx * dv;
+#pragma unroll
+    for (int i = 0; i < kWaMaxPerLane; ++i) {
+      const int dd = lane + 32 * i;
+      if (dd < dv) pa[dd] = acc[i];
+    }
+    if (lane == 0) { part_ml[idx * 2] = m; part_ml[idx * 2 + 1] = l; }
+  }
+}
+
+// out = sum_z e^{m_z - M} acc_z / sum_z e^{m_z - M} l_z over the parts of the key list, in the order of the parts.
+template <typename T>
+__global__ void __launch_bounds__(kWaWarps * 32)
+window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
+                              int out_stride, int H, int dv, int splits, int tokens) {
+  pdl_wait();
+  pdl_launch_dependents();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const long long pair = (long long)blockIdx.x * kWaWarps + warp;
+  if (pair >= (long long)tokens * H) return;
+  const int t = (int)(pair / H), h = (int)(pair % H);
+  const size_t idx0 = ((size_t)t * H + h) * splits;
+  float M = -INFINITY;
+  for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
+  float L = 0.f;
+  float acc[kWaMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kWaMaxPerLane; ++i) acc[i] = 0.f;
+  for (int z = 0; z < splits; ++z) {
+    const float mz = part_ml[(idx0 + z) * 2];
+    if (!(mz > -INFINITY)) continue;
+    const float wz = expf(mz - M);
+    L = fmaf(wz, part_ml[(idx0 + z) * 2 + 1], L);
+    const float* pa = part_acc + (idx0 + z) * dv;
+#pragma unroll
+    for (int i = 0; i < kWaMaxPerLane; ++i) {
+      const int dd = lane + 32 * i;
+      if (dd < dv) acc[i] = fmaf(wz, pa[dd], acc[i]);
+    }
+  }
+  const float inv = L > 0.f ? 1.0f / L : 0.f;
+  T* o = out + (size_t)t * out_stride + (size_t)h * dv;
+#pragma unroll
+  for (int i = 0; i < kWaMaxPerLane; ++i) {
+    const int dd = lane + 32 * i;
+    if (dd < dv) o[dd] = from_f32<T>(acc[i] * inv);
+  }
+}
+
+template <typename T>
+int window_attention(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req,
+                     const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride,
+                     int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep, int splits,
+                     int num_pages, void* stream) {
+  PTL_REQUIRE(tokens >= 0 && H > 0 && G > 0 && page_size > 0 && d > 0, "window_attention: bad sizes");
+  PTL_REQUIRE(H % G == 0, "window_attention: %d query heads are no multiple of %d kv heads", H, G);
+  PTL_REQUIRE(dv >= 1 && dv <= 32 * kWaMaxPerLane, "window_attention: value heads of %d, at most %d", dv, 32 * kWaMaxPerLane);
+  PTL_REQUIRE(d <= 2048, "window_attention: head size %d", d);
+  PTL_REQUIRE(splits >= 1 && splits <= 65535, "window_attention: splits=%d", splits);
+  PTL_REQUIRE(splits == 1 || (part_acc && part_ml), "window_attention: splits > 1 need scratch buffers");
+  PTL_REQUIRE(window >= 0 && keep >= 0 && num_pages > 0, "window_attention: window and kept positions must be >= 0");
+  if (tokens == 0) return 0;
+  constexpr int VN = Vec16<T>::N;
+  const int vec_ok = aligned16(cache) && d % VN == 0 && ((size_t)page_size * G * (d + dv)) % VN == 0 &&
+                     ((size_t)G * page_size * d) % VN == 0;
+  dim3 grid(tokens, (H + kWaWarps - 1) / kWaWarps, splits);
+  const size_t smem = (size_t)kWaWarps * d * sizeof(float);
+  int rc = launch_kernel("window_attention", window_attention_kernel<T>, grid, dim3(kWaWarps * 32), smem, as_stream(stream),
+                         (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req, positions, q_stride,
+                         out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages, vec_ok);
+  if (rc) return rc;
+  if (splits > 1) {
+    const long long pairs = (long long)tokens * H;
+    rc = launch_kernel("window_attention_merge", window_attention_merge_kernel<T>,
+                       dim3((unsigned)((pairs + kWaWarps - 1) / kWaWarps)), dim3(kWaWarps * 32), 0, as_stream(stream), (T*)out,
+                       (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens);
+  }
+  return rc;
+}
+
+}  // namespace ptl
+
+#define PTL_WINDOW_ATTENTION(SUFFIX, TYPE)                                                                                         \
+  PTL_EXPORT int ptl_qk_norm_rotate_store##SUFFIX(void* proj, int tokens, int ld, int H, int G, int d, int dv, const float* wq,     \
+                                                  const float* wk, float eps, const int* positions, const float* freq, int dims,   \
+                                                  float amplitude, const int* slots, void* cache, int page_size,                   \
+                                                  long long num_slots, void* stream) {                                             \
+    return ptl::qk_norm_rotate_store<TYPE>(proj, tokens, ld, H, G, d, dv, wq, wk, eps, positions, freq, dims, amplitude, slots,     \
+                                           cache, page_size, num_slots, stream);                                                   \
+  }                                                                                                                                \
+  PTL_EXPORT int ptl_window_attention##SUFFIX(void* out, const void* q, const void* cache, const int* block_table,                  \
+                                              const int* tok_req, const int* positions, float* part_acc, float* part_ml,           \
+                                              int tokens, int q_stride, int out_stride, int bt_stride, int H, int G, int d, int dv, \
+                                              int page_size, float scale, int window, int keep, int splits, int num_pages,         \
+                                              void* stream) {                                                                      \
+    return ptl::window_attention<TYPE>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride,        \
+                                       out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages,      \
+                                       stream);                                                                                    \
+  }
+PTL_WINDOW_ATTENTION(_f32, float)
+PTL_WINDOW_ATTENTION(_bf16, __nv_bfloat16)

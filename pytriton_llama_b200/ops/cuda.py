@@ -42,6 +42,16 @@ _SIGNATURES = {
     "ptl_kv_write_normed": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ll, _c_f, _ptr],
     "ptl_chunk_attention": [_ptr, _c_int, _c_int, _ptr, _c_int, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _c_int, _c_int, _c_int,
                             _c_int, _c_int, _c_int, _c_f, _c_int, _ptr, _ptr, _ptr, _c_int, _c_int, _c_f, _ptr],
+    "ptl_stream_mix_norm": [_ptr, _ptr, _ptr, _ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_f, _ptr],
+    "ptl_gelu_tanh": [_ptr, _ptr, _c_ll, _ptr],
+    "ptl_qk_norm_rotate_store": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _c_int, _c_f, _ptr,
+                                 _ptr, _c_int, _c_ll, _ptr],
+    "ptl_window_attention": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                             _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _ptr],
+    "ptl_gla_scan": [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr],
+    "ptl_moe_gather": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr],
+    "ptl_moe_grouped": [_ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
+    "ptl_moe_combine": [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr],
     "ptl_paged_attention_simt": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int,
                                  _c_int, _c_int, _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr],
 }
@@ -137,6 +147,12 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_sample_work_words.restype = _c_int
     lib.ptl_softcap.argtypes = [_ptr, _c_ll, _c_f, _ptr]
     lib.ptl_softcap.restype = _c_int
+    lib.ptl_moe_tile_rows.argtypes = []
+    lib.ptl_moe_tile_rows.restype = _c_int
+    lib.ptl_moe_route.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
+    lib.ptl_moe_route.restype = _c_int
+    lib.ptl_moe_plan.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
+    lib.ptl_moe_plan.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
     lib.ptl_set_dependent_launch.argtypes = [_c_int]
     lib.ptl_get_dependent_launch.restype = _c_int
@@ -236,6 +252,8 @@ class CudaOps:
         "_qkv_rope_product": "product", "rope_kv_write": "rope", "_rope_table": "rope",
         "paged_attention": "attention", "_attention_tensor_cores": "attention",
         "sample": "sampling", "token_logprobs": "sampling",
+        "stream_mix_norm": "norm", "gelu_tanh": "elementwise", "qk_norm_rotate_store": "rope", "window_attention": "attention",
+        "gla_scan": "recurrent", "routed_experts": "experts",
     }
 
     def enable_timing(self) -> None:
@@ -971,6 +989,183 @@ class CudaOps:
         self._check(fn(_p(out), out.shape[1], int(column), _p(qkv), qkv.shape[1], _p(bias), _p(cache), _p(block_table),
                        block_table.shape[1], _p(tok_req), _p(positions), qkv.shape[0], H, G, d, dv, page_size, float(scale),
                        int(chunk), _p(r1), _p(r2), _p(talk), max_keys, cache.shape[0], float(out_scale), self._stream()))
+
+    # ------------------------------------------------------------------ copies of the stream, windowed attention, gated linear attention, experts
+    def stream_mix_norm(self, streams: Optional[torch.Tensor], init: Optional[torch.Tensor], y: Optional[torch.Tensor],
+                        mix: Optional[torch.Tensor], out: Optional[torch.Tensor], read: torch.Tensor, weight: torch.Tensor, eps: float,
+                        n_streams: int, rows: Optional[torch.Tensor], dtype: torch.dtype):
+        """The write of a sub-layer's output ``y`` to the copies of the stream (float32 [T, S, width], in place:
+        new_t = sum_s mix[s, t] old_s + out[t] y) and the read of the next one, u = sum_t read[t] new_t, through an RMS
+        norm: (normed [T, width] in ``dtype``, streams).  ``streams`` None: the copies start as ``init`` [T, width].
+        With ``rows`` (int32) only those rows are worked and nothing is stored."""
+        if streams is None:
+            self._want(init, "init", dtype)
+            streams = self.empty((init.shape[0], n_streams, init.shape[1]), torch.float32)
+        else:
+            self._want(streams, "streams", torch.float32)
+            init = None
+        T, S, width = streams.shape
+        if S != n_streams:
+            raise KernelError(f"stream_mix_norm: {S} copies of the stream, expected {n_streams}")
+        y_f32 = 0
+        if y is not None:
+            y_f32 = int(y.dtype == torch.float32 and dtype != torch.float32)
+            self._want(y, "y", torch.float32 if y_f32 else dtype)
+            self._want(mix, "mix", torch.float32)
+            self._want(out, "out", torch.float32)
+            if tuple(y.shape) != (T, width) or tuple(mix.shape) != (S, S) or out.shape[0] != S:
+                raise KernelError("stream_mix_norm: shapes do not fit")
+        self._want(read, "read", torch.float32)
+        self._want(weight, "norm weight", torch.float32)
+        if rows is not None:
+            self._want(rows, "rows", torch.int32)
+        n_out = rows.shape[0] if rows is not None else T
+        normed = self.empty((n_out, width), dtype)
+        fn = getattr(self.lib, "ptl_stream_mix_norm" + _suffix(dtype))
+        self._check(fn(_p(normed), _p(streams), _p(init), _p(y), y_f32, _p(mix) if y is not None else None,
+                       _p(out) if y is not None else None, _p(read), _p(weight), _p(rows), n_out, S, width, float(eps), self._stream()))
+        return normed, streams
+
+    def gelu_tanh(self, x: torch.Tensor) -> torch.Tensor:
+        """0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), float32 inside."""
+        self._want(x, "x")
+        out = torch.empty_like(x)
+        fn = getattr(self.lib, "ptl_gelu_tanh" + _suffix(x.dtype))
+        self._check(fn(_p(out), _p(x), x.numel(), self._stream()))
+        return out
+
+    def qk_norm_rotate_store(self, proj: torch.Tensor, H: int, G: int, d: int, dv: int, q_norm: Optional[torch.Tensor],
+                             k_norm: Optional[torch.Tensor], eps: float, positions: torch.Tensor, freq: Optional[torch.Tensor],
+                             dims: int, amplitude: float, slots: Optional[torch.Tensor], cache: Optional[torch.Tensor],
+                             page_size: int) -> None:
+        """On proj [T, q | k | v] (H heads of d, G of d, G of dv; G = 0: queries only), in place: RMS norm of the whole
+        q and of the whole k part with their weights (eps > 0), rotation of the pairs (2i, 2i+1), i < dims/2, of every
+        head by position * freq[i] with cos and sin times ``amplitude``; k and v go to the tokens' slots of a cache
+        whose pages hold keys, then values."""
+        self._want(proj, "proj")
+        self._want(positions, "positions", torch.int32)
+        for name, t in (("q norm", q_norm), ("k norm", k_norm), ("freq", freq)):
+            if t is not None:
+                self._want(t, name, torch.float32)
+        num_slots = 0
+        if G and cache is not None:
+            self._want(cache, "cache", proj.dtype)
+            self._want(slots, "slots", torch.int32)
+            if cache[0].numel() != G * page_size * (d + dv):
+                raise KernelError("qk_norm_rotate_store: the cache's pages do not fit the heads")
+            num_slots = cache.shape[0] * page_size
+        if freq is not None and freq.numel() < dims // 2:
+            raise KernelError("qk_norm_rotate_store: fewer frequencies than pairs")
+        fn = getattr(self.lib, "ptl_qk_norm_rotate_store" + _suffix(proj.dtype))
+        self._check(fn(_p(proj), proj.shape[0], proj.shape[1], H, G, d, dv, _p(q_norm), _p(k_norm), float(eps), _p(positions),
+                       _p(freq), int(dims) if freq is not None else 0, float(amplitude), _p(slots) if G else None,
+                       _p(cache) if G else None, page_size, num_slots, self._stream()))
+
+    def window_attention(self, q: torch.Tensor, cache: torch.Tensor, block_table: torch.Tensor, tok_req: torch.Tensor,
+                         positions: torch.Tensor, H: int, G: int, d: int, dv: int, page_size: int, scale: float, window: int = 0,
+                         keep_first: int = 0, splits: int = 1, hints=None) -> torch.Tensor:
+        """Softmax attention of every token over the keys j <= p of its request with p - j < window or j < keep_first
+        (window 0: all); q is [T, >= H*d], the result [T, H*dv]."""
+        self._want(q, "q")
+        self._want(cache, "cache", q.dtype)
+        for name, t in (("block_table", block_table), ("tok_req", tok_req), ("positions", positions)):
+            self._want(t, name, torch.int32)
+        if cache[0].numel() != G * page_size * (d + dv):
+            raise KernelError("window_attention: the cache's pages do not fit the heads")
+        tokens = q.shape[0]
+        out = self.empty((tokens, H * dv), q.dtype)
+        if (q.dtype == torch.bfloat16 and d == dv and d in (64, 128) and self._work(hints, "prefill_tiles") is not None
+                and self._work(hints, "decode_items") is not None and os.environ.get("PTL_WINDOW_TC", "1") != "0"):
+            if self._window_attention_tensor_cores(out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale,
+                                                   window, keep_first, hints):
+                return out
+        longest = getattr(hints, "max_ctx_len", 0) or block_table.shape[1] * page_size
+        if window:
+            longest = min(longest, window + keep_first)
+        splits = self._window_splits(tokens, H, longest)
+        self._window_attention_simt(out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
+                                    keep_first, splits, None)
+        return out
+
+    def _window_splits(self, tokens: int, H: int, longest: int) -> int:
+        """Parts of a token's key list for the CUDA-core kernel: enough warps to fill the SMs, at least 64 keys each."""
+        warps = max(1, tokens * H)
+        return int(max(1, min(longest // 64, (self._sm_count * 16) // warps, 64)))
+
+    def _window_attention_simt(self, out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
+                               keep_first, splits, rows) -> None:
+        tokens = q.shape[0]
+        part_acc = part_ml = None
+        if splits > 1:
+            part_acc = self.empty((tokens, H, splits, dv), torch.float32)
+            part_ml = self.empty((tokens, H, splits, 2), torch.float32)
+        fn = getattr(self.lib, "ptl_window_attention" + _suffix(q.dtype))
+        self._check(fn(_p(out), _p(q), _p(cache), _p(block_table), _p(tok_req), _p(positions), _p(part_acc), _p(part_ml), tokens,
+                       q.shape[1], out.shape[1], block_table.shape[1], H, G, d, dv, page_size, float(scale), int(window),
+                       int(keep_first), int(splits), cache.shape[0], self._stream()), kernels=2 if splits > 1 else 1)
+
+    def _window_attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale, window,
+                                       keep_first, hints) -> bool:
+        return False
+
+    def gla_scan(self, proj: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, inv_tau: float, state: torch.Tensor, ctx, H: int,
+                 d: int, dv: int, q_scale: float) -> torch.Tensor:
+        """The recurrence of ``parts/gla.py``: proj [T, q | k | v | ...], z float32 [T, H*d] (the decay's argument before
+        its bias); state float32 [slots, H, d, dv]; returns the heads' read-outs, float32 [T, H*dv]."""
+        self._want(proj, "proj")
+        for name, t in (("z", z), ("bias", bias), ("state", state)):
+            self._want(t, name, torch.float32)
+        if z.shape[1] != H * d or bias.shape[0] != H * d or tuple(state.shape[1:]) != (H, d, dv):
+            raise KernelError("gla_scan: shapes do not fit")
+        out = self.empty((proj.shape[0], H * dv), torch.float32)
+        fn = getattr(self.lib, "ptl_gla_scan" + _suffix(proj.dtype))
+        self._check(fn(_p(out), _p(proj), proj.shape[1], _p(z), _p(bias), float(inv_tau), _p(state), _p(ctx.q_start), _p(ctx.positions),
+                       _p(ctx.state_slot), ctx.num_requests, H, d, dv, float(q_scale), self._stream()))
+        return out
+
+    moe_tensor_cores = os.environ.get("PTL_MOE_TC", "1") != "0"
+
+    def routed_experts(self, x: torch.Tensor, logits: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
+                       scale_input: bool, shared: Optional[torch.Tensor]) -> torch.Tensor:
+        """x [T, width], router logits float32 [T, E], expert weights [E, 2*inter, width] (gate rows, then up rows) and
+        [E, width, inter]: every token's ``top`` experts by sigmoid(logit), weighted by that score on the expert's input
+        (``scale_input``) or output, summed, plus ``shared`` [T, width]; float32 [T, width].  Five kernels and no word
+        back to the host: route, plan (sort by expert), gather, two grouped products, combine."""
+        self._want(x, "x")
+        self._want(logits, "logits", torch.float32)
+        self._want(w_gate_up, "expert gate/up weights", x.dtype)
+        self._want(w_down, "expert down weights", x.dtype)
+        if shared is not None:
+            self._want(shared, "shared", x.dtype)
+        T, width = x.shape
+        E, two_inter, _ = w_gate_up.shape
+        inter = two_inter // 2
+        if logits.shape[1] != E or tuple(w_down.shape) != (E, width, inter) or w_gate_up.shape[2] != width:
+            raise KernelError("routed_experts: shapes do not fit")
+        n = T * top
+        tile = self.lib.ptl_moe_tile_rows()
+        max_tiles = -(-n // tile) + min(E, n)
+        stream = self._stream()
+        ints = self.empty((2 * n + 3 * max_tiles + 4,), torch.int32)
+        ids, pos, tiles, meta = ints[:n], ints[n:2 * n], ints[2 * n:2 * n + 3 * max_tiles], ints[2 * n + 3 * max_tiles:]
+        weights = self.empty((n,), torch.float32)
+        self._check(self.lib.ptl_moe_route(_p(ids), _p(weights), _p(logits), T, E, top, stream))
+        self._check(self.lib.ptl_moe_plan(_p(pos), _p(tiles), _p(meta), _p(ids), n, E, max_tiles, stream))
+        rows = max_tiles * tile
+        sorted_x = self.empty((rows, width), x.dtype)
+        sfx = _suffix(x.dtype)
+        self._check(getattr(self.lib, "ptl_moe_gather" + sfx)(_p(sorted_x), _p(x), _p(pos), _p(weights), n, top, width,
+                                                              int(bool(scale_input)), stream))
+        hidden = self.empty((rows, inter), x.dtype)
+        tc = int(self.moe_tensor_cores)
+        grouped = getattr(self.lib, "ptl_moe_grouped" + sfx)
+        self._check(grouped(_p(hidden), inter, _p(sorted_x), _p(w_gate_up), _p(tiles), _p(meta), max_tiles, two_inter, width, 1, tc, stream))
+        y = self.empty((rows, width), torch.float32)
+        self._check(grouped(_p(y), width, _p(hidden), _p(w_down), _p(tiles), _p(meta), max_tiles, width, inter, 0, tc, stream))
+        out = self.empty((T, width), torch.float32)
+        self._check(getattr(self.lib, "ptl_moe_combine" + sfx)(_p(out), _p(y), _p(shared), _p(pos), _p(weights), T, top, width,
+                                                               int(bool(scale_input)), stream))
+        return out
 
     def token_logprobs(self, logits: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
         """log softmax(logits[row])[tokens[row]] as float32 [rows]."""
