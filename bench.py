@@ -2,6 +2,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --family tibepel      # another workload: the Tibepel decoder beside a Llama of equal size
+    python bench.py --family lilenex      # likewise the Lilenex decoder
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and context 4096, timed on
 the device with CUDA events around exactly K decode steps (a step = the engine's step function for
@@ -169,9 +170,32 @@ def _tibepel(width, layers, ff, vocab):
                        for i in range(layers)]}
 
 
+def _lilenex(width, layers, ff, vocab):
+    """A Lilenex of sizes that resemble a real model's layers: two copies of the stream; of every four layers the second
+    is gated linear attention (heads of 128 x 128), the third attends over the keys and values of the first; attention
+    with heads of 128, 4 query heads per kv head, a window of 1,024 positions that keeps the first 4, half of every head
+    rotated with YaRN-scaled frequencies; the first layer's feed-forward dense, the others 16 experts of ff/4 with two
+    per token beside a shared one of ff/2 (as many weights at work per token as the dense layer has)."""
+    heads = width // 128
+    rot = {"dims": 64, "base": 1000000.0, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}
+    att = {"heads": heads, "kv_heads": max(1, heads // 4), "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+           "mask": {"size": 1024, "keep_first": 4}, "rot": rot}
+    gla = {"heads": heads, "dim": 128, "vdim": 128, "tau": 16.0, "rank": 16}
+    moe = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 2}, "shared": {"ff": ff // 2}}
+    out = []
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff} if i == 0 else moe
+        if i % 4 == 1:
+            out.append({"type": "gla", "mixer": gla, "mlp": mlp})
+        else:
+            out.append({"type": "attention", "mixer": dict(att, kv_from=i - 2) if i % 4 == 2 else att, "mlp": mlp})
+    return {"architecture": "Lilenex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "residual_mult": 0.5, "streams": 2,
+            "layers": out}
+
+
 def family_bench(args) -> int:
-    """``--family tibepel``: prefill (one step of 2,048 prompt tokens, as one prompt and as 8 prompts of 256) and decode
-    (8 requests at 1,024 tokens, a step with its sampling kernel) of the Tibepel decoder and of a Llama decoder of the same width, depth, feed-forward size
+    """``--family tibepel`` or ``--family lilenex``: prefill (one step of 2,048 prompt tokens, as one prompt and as 8 prompts of 256) and decode
+    (8 requests at 1,024 tokens, a step with its sampling kernel) of that decoder and of a Llama decoder of the same width, depth, feed-forward size
     and vocabulary, on random weights, timed with CUDA events after warm-up; then one timed step of each kind with
     every operator bracketed by events, for the milliseconds by class of kernels.  One JSON line."""
     import torch
@@ -187,7 +211,7 @@ def family_bench(args) -> int:
     toks = lambda n: torch.randint(0, vocab, (n,), generator=gen).tolist()
     rows = []
     for width, layers, ff in sizes:
-        models = {"tibepel": _tibepel(width, layers, ff, vocab),
+        models = {args.family: (_tibepel if args.family == "tibepel" else _lilenex)(width, layers, ff, vocab),
                   "llama": dict(_llama(layers, width, width // 128, max(1, width // 512), 128, ff, 32.0, False), vocab_size=vocab)}
         row = {"width": width, "layers": layers, "ff": ff, "vocab": vocab}
         for name, cfg in models.items():
@@ -259,7 +283,7 @@ def family_bench(args) -> int:
             del engine
             torch.cuda.empty_cache()
         rows.append(row)
-    print(json.dumps({"metric": "family_tokens_per_s", "family": "tibepel", "beside": "llama of equal width, depth, feed-forward and vocabulary",
+    print(json.dumps({"metric": "family_tokens_per_s", "family": args.family, "beside": "llama of equal width, depth, feed-forward and vocabulary",
                       "dtype": args.dtype, "data": "synthetic", "n_gpus": 1, "steps": K, "warmup": W,
                       "workload": {"prefill_tokens": prompt_len, "decode_batch": batch, "decode_context": context},
                       "peaks": dict(peaks, kind=peak_kind), "sizes": rows}))
@@ -303,7 +327,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=None, help="decode batch (default: 8; 32 for 3b; 64 for 8b)")
     ap.add_argument("--layers", type=int, default=None, help="fewer layers than the model has (named in config)")
     ap.add_argument("--points", default=None, help="extra decode batch sizes, comma separated ('' for none)")
-    ap.add_argument("--family", default=None, choices=["tibepel"],
+    ap.add_argument("--family", default=None, choices=["tibepel", "lilenex"],
                     help="another workload: this decoder beside a Llama of equal size, prefill and decode (own JSON line)")
     ap.add_argument("--family-sizes", default=None, help="with --family: WIDTHxLAYERSxFF[,...] (default 1024x8x4096,2048x8x8192)")
     ap.add_argument("--no-e2e", action="store_true")

@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(PrefillCfg<D, MT>::kThreads)
 prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ q,
                          const __nv_bfloat16* __restrict__ cache, const int* __restrict__ block_table,
                          const int* __restrict__ tiles, int q_stride, int out_stride, int bt_stride, int nq,
-                         int nkv, int page_size, float scale_log2, int window, int num_pages, int page_shift) {
+                         int nkv, int page_size, float scale_log2, int window, int num_pages, int page_shift, int keep) {
   using Cfg = PrefillCfg<D, MT>;
   extern __shared__ __align__(128) unsigned char smem[];
   __shared__ int s_pages[kPfStagedPages];
@@ -57,14 +57,18 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   const int kvh = h / (nq / nkv);
   const int k_lo = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int k_end = pos0 + rows;                 // one past the last key any row of the tile sees
-  const int ntiles = (k_end - k_lo + kPfKeys - 1) / kPfKeys;
+  // positions below `keep` stay visible when the window has passed them: those before the first window of the
+  // tile come first, in key tiles of their own (no key is met twice), then the keys from k_lo on
+  const int keep_lim = min(keep, k_lo);
+  const int n_keep_tiles = (keep_lim + kPfKeys - 1) / kPfKeys;
+  const int ntiles = n_keep_tiles + (k_end - k_lo + kPfKeys - 1) / kPfKeys;
   const int* bt_global = block_table + (size_t)req * bt_stride;
   const size_t plane = (size_t)nkv * page_size * D;
   const uint32_t q_smem = smem_u32(smem);
   const uint32_t kv_smem = q_smem + Cfg::kQBytes;
 
   // block-table entries of the key range in shared memory (when they fit)
-  const int first_block = k_lo / page_size;
+  const int first_block = n_keep_tiles ? 0 : k_lo / page_size;
   const int n_blocks = (k_end - 1) / page_size - first_block + 1;
   const bool staged = n_blocks <= kPfStagedPages;
   if (staged) {
@@ -80,12 +84,13 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
   auto load_tile = [&](int tile, int stage) {
     const uint32_t kbase = kv_smem + stage * 2 * Cfg::kTileBytes;
     const uint32_t vbase = kbase + Cfg::kTileBytes;
-    const int k0 = k_lo + tile * kPfKeys;
+    const int k0 = tile < n_keep_tiles ? tile * kPfKeys : k_lo + (tile - n_keep_tiles) * kPfKeys;
+    const int k_limit = tile < n_keep_tiles ? keep_lim : k_end;
 #pragma unroll
     for (int i = 0; i < kPasses; ++i) {
       const int row = my_row + i * kRowsPerPass;
       const int key = k0 + row;
-      bool valid = key < k_end;
+      bool valid = key < k_limit;
       int page, off;
       if (fast_pages) {
         page = valid ? bt[key >> page_shift] : 0;
@@ -150,9 +155,10 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
       if (nxt < ntiles) load_tile(nxt, nxt % Cfg::kStages);
       cp_async_commit();
     }
-    const int key_first = k_lo + tile * kPfKeys;
+    const bool keep_tile = tile < n_keep_tiles;
+    const int key_first = keep_tile ? tile * kPfKeys : k_lo + (tile - n_keep_tiles) * kPfKeys;
     if (key_first > warp_qmax) continue;                       // wholly above this warp's diagonal
-    if (window > 0 && key_first + kPfKeys - 1 < warp_qmin - window + 1) continue;   // wholly before its window
+    if (!keep_tile && window > 0 && key_first >= keep && key_first + kPfKeys - 1 < warp_qmin - window + 1) continue;   // wholly before its window
     const int stage = tile % Cfg::kStages;
     const uint32_t kbase = kv_smem + stage * 2 * Cfg::kTileBytes;
     const uint32_t vbase = kbase + Cfg::kTileBytes;
@@ -177,8 +183,8 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
         }
       }
     }
-    const bool need_mask = (key_first + kPfKeys - 1 > warp_qmin) ||
-                           (window > 0 && key_first < warp_qmax - window + 1);
+    const bool need_mask = keep_tile ? (key_first + kPfKeys > keep_lim)
+                                     : ((key_first + kPfKeys - 1 > warp_qmin) || (window > 0 && key_first < warp_qmax - window + 1));
     uint32_t pa[MT][kPfKeys / 16][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
@@ -191,7 +197,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
           if (need_mask) {
             const int key = key_first + nt * 8 + 2 * c + (e & 1);
             const int qp = qpos0 + (e >> 1) * 8;
-            if (key > qp || (window > 0 && key < qp - window + 1)) v = -INFINITY;
+            if (keep_tile ? key >= keep_lim : (key > qp || (window > 0 && key < qp - window + 1 && key >= keep))) v = -INFINITY;
           }
           s[mt][nt][e] = v;
         }
@@ -257,7 +263,7 @@ prefill_attention_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* _
 template <int D, int MT>
 int launch_prefill(void* out, const void* q, const void* cache, const int* block_table, const int* tiles, int n_tiles,
                    int q_stride, int out_stride, int bt_stride, int nq, int nkv, int page_size, float scale,
-                   int window, int num_pages, void* stream) {
+                   int window, int num_pages, void* stream, int keep = 0) {
   using Cfg = PrefillCfg<D, MT>;
   static SmemRaised raised = {};
   if (int rc = raise_shared_memory("prefill_attention", prefill_attention_kernel<D, MT>, Cfg::kSmem, raised)) return rc;
@@ -268,7 +274,7 @@ int launch_prefill(void* out, const void* q, const void* cache, const int* block
   return launch_kernel("prefill_attention", prefill_attention_kernel<D, MT>, grid, dim3(Cfg::kThreads), Cfg::kSmem,
                        as_stream(stream), (__nv_bfloat16*)out, (const __nv_bfloat16*)q, (const __nv_bfloat16*)cache,
                        block_table, tiles, q_stride, out_stride, bt_stride, nq, nkv, page_size,
-                       scale * 1.4426950408889634f, window, num_pages, page_shift);
+                       scale * 1.4426950408889634f, window, num_pages, page_shift, keep);
 }
 
 }  // namespace ptl
@@ -290,4 +296,24 @@ PTL_EXPORT int ptl_prefill_attention_bf16(void* out, const void* q, const void* 
                                  page_size, scale, window, num_pages, stream);
   return launch_prefill<128, 1>(out, q, cache, block_table, tiles, n_tiles, q_stride, out_stride, bt_stride, nq, nkv,
                                 page_size, scale, window, num_pages, stream);
+}
+
+// The same with positions below `keep` visible to every later query whatever the window (0: none).
+PTL_EXPORT int ptl_prefill_attention_keep_bf16(void* out, const void* q, const void* cache, const int* block_table,
+                                               const int* tiles, int n_tiles, int q_stride, int out_stride, int bt_stride,
+                                               int nq, int nkv, int d, int page_size, float scale, int window, int keep,
+                                               int num_pages, void* stream) {
+  using namespace ptl;
+  PTL_REQUIRE(n_tiles >= 0 && nq > 0 && nkv > 0 && page_size > 0 && num_pages > 0 && keep >= 0, "prefill_attention: bad sizes");
+  PTL_REQUIRE(nq % nkv == 0, "prefill_attention: %d query heads are no multiple of %d kv heads", nq, nkv);
+  if (d != 64 && d != 128) return -2;
+  PTL_REQUIRE(aligned16(q) && aligned16(cache) && aligned16(out) && q_stride % 8 == 0 && out_stride % 2 == 0,
+              "prefill_attention: q, cache and out must be 16-byte aligned");
+  if (n_tiles == 0) return 0;
+  if (window == 0) keep = 0;
+  if (d == 64)
+    return launch_prefill<64, PTL_PF_MT>(out, q, cache, block_table, tiles, n_tiles, q_stride, out_stride, bt_stride, nq, nkv,
+                                         page_size, scale, window, num_pages, stream, keep);
+  return launch_prefill<128, 1>(out, q, cache, block_table, tiles, n_tiles, q_stride, out_stride, bt_stride, nq, nkv,
+                                page_size, scale, window, num_pages, stream, keep);
 }

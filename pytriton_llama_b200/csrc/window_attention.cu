@@ -17,6 +17,8 @@
 // list (the kept ones that the window has passed, then the window), 32 at a time, one key per
 // lane; scores, softmax and the weighted sum of values are float32, with float32 inputs compensated
 // (see attention_simt.cu).  The list may be split over blockIdx.z and merged by a second kernel.
+// The kernel works `tokens` rows, or the rows that `items` names (the single tokens of a step
+// whose longer portions another kernel takes); partial results are indexed by the row itself.
 #include "common.cuh"
 
 namespace ptl {
@@ -134,12 +136,12 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
                         const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
                         const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride, int out_stride,
                         int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep,
-                        int splits, int num_pages, int vec_ok) {
+                        int splits, int num_pages, int vec_ok, const int* __restrict__ items) {
   extern __shared__ float qs_all[];  // [warps][d]
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t = blockIdx.x;
+  const int t = items ? items[blockIdx.x] : blockIdx.x;
   const int h = blockIdx.y * kWaWarps + warp;
   if (h >= H) return;
   const int split = blockIdx.z;
@@ -260,13 +262,14 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
 template <typename T>
 __global__ void __launch_bounds__(kWaWarps * 32)
 window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ part_acc, const float* __restrict__ part_ml,
-                              int out_stride, int H, int dv, int splits, int tokens) {
+                              int out_stride, int H, int dv, int splits, int tokens, const int* __restrict__ items) {
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const long long pair = (long long)blockIdx.x * kWaWarps + warp;
   if (pair >= (long long)tokens * H) return;
-  const int t = (int)(pair / H), h = (int)(pair % H);
+  const int t = items ? items[pair / H] : (int)(pair / H);
+  const int h = (int)(pair % H);
   const size_t idx0 = ((size_t)t * H + h) * splits;
   float M = -INFINITY;
   for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
@@ -299,7 +302,7 @@ template <typename T>
 int window_attention(void* out, const void* q, const void* cache, const int* block_table, const int* tok_req,
                      const int* positions, float* part_acc, float* part_ml, int tokens, int q_stride, int out_stride,
                      int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep, int splits,
-                     int num_pages, void* stream) {
+                     int num_pages, const int* items, void* stream) {
   PTL_REQUIRE(tokens >= 0 && H > 0 && G > 0 && page_size > 0 && d > 0, "window_attention: bad sizes");
   PTL_REQUIRE(H % G == 0, "window_attention: %d query heads are no multiple of %d kv heads", H, G);
   PTL_REQUIRE(dv >= 1 && dv <= 32 * kWaMaxPerLane, "window_attention: value heads of %d, at most %d", dv, 32 * kWaMaxPerLane);
@@ -315,13 +318,13 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
   const size_t smem = (size_t)kWaWarps * d * sizeof(float);
   int rc = launch_kernel("window_attention", window_attention_kernel<T>, grid, dim3(kWaWarps * 32), smem, as_stream(stream),
                          (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req, positions, q_stride,
-                         out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages, vec_ok);
+                         out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages, vec_ok, items);
   if (rc) return rc;
   if (splits > 1) {
     const long long pairs = (long long)tokens * H;
     rc = launch_kernel("window_attention_merge", window_attention_merge_kernel<T>,
                        dim3((unsigned)((pairs + kWaWarps - 1) / kWaWarps)), dim3(kWaWarps * 32), 0, as_stream(stream), (T*)out,
-                       (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens);
+                       (const float*)part_acc, (const float*)part_ml, out_stride, H, dv, splits, tokens, items);
   }
   return rc;
 }
@@ -340,10 +343,10 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
                                               const int* tok_req, const int* positions, float* part_acc, float* part_ml,           \
                                               int tokens, int q_stride, int out_stride, int bt_stride, int H, int G, int d, int dv, \
                                               int page_size, float scale, int window, int keep, int splits, int num_pages,         \
-                                              void* stream) {                                                                      \
+                                              const int* items, void* stream) {                                                                      \
     return ptl::window_attention<TYPE>(out, q, cache, block_table, tok_req, positions, part_acc, part_ml, tokens, q_stride,        \
                                        out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages,      \
-                                       stream);                                                                                    \
+                                       items, stream);                                                                                    \
   }
 PTL_WINDOW_ATTENTION(_f32, float)
 PTL_WINDOW_ATTENTION(_bf16, __nv_bfloat16)

@@ -47,7 +47,7 @@ _SIGNATURES = {
     "ptl_qk_norm_rotate_store": [_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _c_int, _c_f, _ptr,
                                  _ptr, _c_int, _c_ll, _ptr],
     "ptl_window_attention": [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                             _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _ptr],
+                             _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _c_int, _ptr, _ptr],
     "ptl_gla_scan": [_ptr, _ptr, _c_int, _ptr, _ptr, _c_f, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_f, _ptr],
     "ptl_moe_gather": [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr],
     "ptl_moe_grouped": [_ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _ptr],
@@ -147,6 +147,9 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_sample_work_words.restype = _c_int
     lib.ptl_softcap.argtypes = [_ptr, _c_ll, _c_f, _ptr]
     lib.ptl_softcap.restype = _c_int
+    lib.ptl_prefill_attention_keep_bf16.argtypes = [_ptr, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                                    _c_int, _c_int, _c_f, _c_int, _c_int, _c_int, _ptr]
+    lib.ptl_prefill_attention_keep_bf16.restype = _c_int
     lib.ptl_moe_tile_rows.argtypes = []
     lib.ptl_moe_tile_rows.restype = _c_int
     lib.ptl_moe_route.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
@@ -1094,19 +1097,39 @@ class CudaOps:
 
     def _window_attention_simt(self, out, q, cache, block_table, tok_req, positions, H, G, d, dv, page_size, scale, window,
                                keep_first, splits, rows) -> None:
+        """``rows``: None for every token row, else (int32 row indices or None for 0..n-1, n)."""
         tokens = q.shape[0]
+        items, n_rows = (None, tokens) if rows is None else rows
         part_acc = part_ml = None
         if splits > 1:
             part_acc = self.empty((tokens, H, splits, dv), torch.float32)
             part_ml = self.empty((tokens, H, splits, 2), torch.float32)
         fn = getattr(self.lib, "ptl_window_attention" + _suffix(q.dtype))
-        self._check(fn(_p(out), _p(q), _p(cache), _p(block_table), _p(tok_req), _p(positions), _p(part_acc), _p(part_ml), tokens,
+        self._check(fn(_p(out), _p(q), _p(cache), _p(block_table), _p(tok_req), _p(positions), _p(part_acc), _p(part_ml), n_rows,
                        q.shape[1], out.shape[1], block_table.shape[1], H, G, d, dv, page_size, float(scale), int(window),
-                       int(keep_first), int(splits), cache.shape[0], self._stream()), kernels=2 if splits > 1 else 1)
+                       int(keep_first), int(splits), cache.shape[0], _p(items), self._stream()), kernels=2 if splits > 1 else 1)
 
     def _window_attention_tensor_cores(self, out, q, cache, block_table, tok_req, positions, H, G, d, page_size, scale, window,
                                        keep_first, hints) -> bool:
-        return False
+        """bfloat16, key and value heads of 64 or 128: the portions of a step on the tensor cores (the warp-level prompt
+        kernel, which walks the kept first keys as key tiles of their own before the window's), its single tokens on
+        the CUDA-core kernel with their key lists split; both write their rows of ``out``."""
+        dec, tiles = hints.work["decode_items"], hints.work["prefill_tiles"]
+        if tiles.items:
+            rc = self.lib.ptl_prefill_attention_keep_bf16(
+                _p(out), _p(q), _p(cache), _p(block_table), _p(tiles.tensor), tiles.items, q.shape[1], H * d, block_table.shape[1],
+                H, G, d, page_size, float(scale), int(window), int(keep_first), cache.shape[0], self._stream())
+            if rc == -2:
+                return False
+            self._check(rc)
+        if dec.items:
+            longest = getattr(hints, "max_ctx_len", 0) or block_table.shape[1] * page_size
+            if window:
+                longest = min(longest, window + keep_first)
+            self._window_attention_simt(out, q, cache, block_table, tok_req, positions, H, G, d, d, page_size, scale, window,
+                                        keep_first, self._window_splits(dec.items, H, longest),
+                                        (None if dec.in_order else dec.tensor, dec.items))
+        return True
 
     def gla_scan(self, proj: torch.Tensor, z: torch.Tensor, bias: torch.Tensor, inv_tau: float, state: torch.Tensor, ctx, H: int,
                  d: int, dv: int, q_scale: float) -> torch.Tensor:

@@ -202,3 +202,153 @@ def forward(cfg: dict, W: Dict[str, torch.Tensor], tokens: List[int], return_lay
     x = rms_norm(sum(xs), W["final.norm"], eps)
     logits = x @ W["embed"].to(F).T
     return (logits, torch.stack(after)) if return_layers else logits
+
+
+# ----------------------------------------------------------------------------- random models for the tests
+def tensor_shapes(cfg: dict, rank: int = 6) -> Dict[str, tuple]:
+    """Name -> shape of every tensor of a model (``rank``: inner size of the decay projections)."""
+    W, S = int(cfg["width"]), int(cfg.get("streams") or 0)
+    out = {"embed": (int(cfg["vocab"]), W), "final.norm": (W,)}
+    for i, L in enumerate(cfg["layers"]):
+        p, m = f"l{i}.", L["mixer"]
+        out[p + "norm1"] = (W,)
+        subs = [1]
+        if L["type"] == "attention":
+            H, G, d, e = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+            out.update({p + "mix.q": (H * d, W), p + "mix.q.norm": (H * d,), p + "mix.o": (W, H * e)})
+            if m.get("kv_from") is None:
+                out.update({p + "mix.k": (G * d, W), p + "mix.v": (G * e, W), p + "mix.k.norm": (G * d,)})
+        else:
+            H, d, e = m["heads"], m["dim"], m["vdim"]
+            out.update({p + "mix.q": (H * d, W), p + "mix.k": (H * d, W), p + "mix.v": (H * e, W), p + "mix.g": (H * e, W),
+                        p + "mix.o": (W, H * e), p + "mix.norm": (e,), p + "mix.a1": (rank, W), p + "mix.a2": (H * d, rank),
+                        p + "mix.a2.b": (H * d,)})
+        mlp = L.get("mlp")
+        if mlp:
+            subs.append(2)
+            out[p + "norm2"] = (W,)
+            if mlp["kind"] == "dense":
+                out.update({p + "mlp.up": (mlp["ff"], W), p + "mlp.down": (W, mlp["ff"])})
+            else:
+                ff = mlp["expert"]["ff"]
+                out[p + "mlp.router"] = (mlp["router"]["experts"], W)
+                for x in range(mlp["router"]["experts"]):
+                    out.update({f"{p}mlp.e{x}.gate": (ff, W), f"{p}mlp.e{x}.up": (ff, W), f"{p}mlp.e{x}.down": (W, ff)})
+                if mlp.get("shared"):
+                    sf = mlp["shared"]["ff"]
+                    out.update({p + "mlp.shared.gate": (sf, W), p + "mlp.shared.up": (sf, W), p + "mlp.shared.down": (W, sf)})
+        for q in subs if S else []:
+            out.update({f"{p}hc{q}.in": (S,), f"{p}hc{q}.out": (S,), f"{p}hc{q}.mix": (S, S)})
+    return out
+
+
+def random_weights(cfg: dict, seed: int, dtype=torch.float32, rank: int = 6) -> Dict[str, torch.Tensor]:
+    """Weights drawn so that no mechanism drowns: matrices N(0, 1.5^2 / fan_in), decays near one, copies of the
+    stream that mix but do not blow up, router logits that spread."""
+    gen = torch.Generator().manual_seed(seed)
+    rand = lambda *s: torch.randn(*s, generator=gen, dtype=torch.float32)
+    uni = lambda lo, hi, *s: lo + (hi - lo) * torch.rand(*s, generator=gen, dtype=torch.float32)
+    out = {}
+    for name, shape in sorted(tensor_shapes(cfg, rank).items()):
+        last = name.split(".")[-1]
+        if name == "embed":
+            t = rand(*shape) * 0.7
+        elif last in ("norm1", "norm2", "norm") or name == "final.norm":
+            t = 1 + 0.2 * rand(*shape)
+        elif last == "in":
+            t = uni(0.2, 0.8, *shape)
+        elif last == "out":
+            t = uni(0.4, 1.0, *shape)
+        elif last == "mix":
+            t = torch.eye(shape[0]) * 0.6 + 0.3 * uni(0, 1, *shape)
+        elif last == "b":
+            t = uni(0.5, 4.0, *shape)
+        elif last == "router":
+            t = rand(*shape) * (3.0 / math.sqrt(shape[-1]))
+        else:
+            t = rand(*shape) * (1.5 / math.sqrt(shape[-1]))
+        out[name] = t.to(dtype)
+    return out
+
+
+def write_model(folder, cfg: dict, seed: int, dtype=torch.float32, weights=None):
+    """A model folder (config.json, model.safetensors); returns the weights as stored."""
+    import json
+    from pathlib import Path
+    from pytriton_llama_b200.weights import write_file      # only the file format comes from the package
+    folder = Path(folder)
+    folder.mkdir(parents=True, exist_ok=True)
+    W = weights if weights is not None else random_weights(cfg, seed, dtype)
+    (folder / "config.json").write_text(json.dumps(cfg))
+    write_file(folder / "model.safetensors", W)
+    return W
+
+
+def attention(heads, kv_heads, dim, vdim, scale, size=0, keep_first=0, rot=None, kv_from=None):
+    m = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": vdim, "scale": scale}
+    if size:
+        m["mask"] = {"size": size, "keep_first": keep_first}
+    if rot:
+        m["rot"] = rot
+    if kv_from is not None:
+        m["kv_from"] = kv_from
+    return m
+
+
+def rotation(dims, base, scaling=None):
+    r = {"dims": dims, "base": base}
+    if scaling:
+        r["scaling"] = dict(zip(("factor", "original", "fast", "slow"), scaling))
+    return r
+
+
+def gla(heads, dim, vdim, tau):
+    return {"heads": heads, "dim": dim, "vdim": vdim, "tau": tau}
+
+
+def dense(ff):
+    return {"kind": "dense", "ff": ff}
+
+
+def moe(ff, experts, top, shared=0):
+    m = {"kind": "moe", "expert": {"ff": ff}, "router": {"experts": experts, "top": top}}
+    if shared:
+        m["shared"] = {"ff": shared}
+    return m
+
+
+def layer(kind, mixer, mlp):
+    return {"type": kind, "mixer": mixer, "mlp": mlp}
+
+
+def config(vocab, width, layers, streams=0, mult=1.0, eps=1e-5):
+    c = {"architecture": "Lilenex", "vocab": vocab, "width": width, "norm": {"eps": eps}, "residual_mult": mult, "layers": layers}
+    if streams:
+        c["streams"] = streams
+    return c
+
+
+_ROT_A = rotation(8, 1000.0, (4.0, 32, 8.0, 1.0))
+# Two copies of the stream; value heads larger than key heads; a layer that reads another's keys through a wider
+# window with more kept positions; two experts per token; a layer without a feed-forward that sees everything and
+# rotates whole heads without scaling; windows that straddle pages of 4, 8 and 16.
+TINY_A = config(97, 48, [
+    layer("attention", attention(4, 2, 16, 24, 0.3, size=11, keep_first=3, rot=_ROT_A), dense(40)),
+    layer("gla", gla(3, 8, 12, 4.0), moe(24, 5, 2, shared=16)),
+    layer("attention", attention(4, 2, 16, 24, 0.25, size=19, keep_first=5, rot=_ROT_A, kv_from=0), moe(16, 4, 1)),
+    layer("attention", attention(2, 1, 24, 16, 0.2, rot=rotation(24, 300.0)), None),
+], streams=2, mult=0.7)
+# One stream with a plain residual sum; a single linear-attention head wider than a warp's packet; as many kv heads as
+# heads, no rotation, no kept positions; every expert chosen; a layer without a feed-forward.
+TINY_B = config(70, 64, [
+    layer("gla", gla(1, 20, 40, 16.0), dense(72)),
+    layer("attention", attention(6, 6, 16, 16, 0.35, size=7), moe(24, 3, 3, shared=24)),
+    layer("gla", gla(2, 32, 8, 2.0), None),
+], eps=3e-4)
+# Four copies; one kv head for three query heads; more kept positions than the window is wide; a reader whose window
+# is narrower than its source's.
+TINY_C = config(50, 32, [
+    layer("attention", attention(3, 1, 16, 32, 0.3, size=8, keep_first=9, rot=rotation(16, 50.0, (2.0, 16, 4.0, 0.5))), moe(16, 6, 2)),
+    layer("attention", attention(3, 1, 16, 32, 0.3, size=5, keep_first=2, rot=rotation(16, 50.0, (2.0, 16, 4.0, 0.5)), kv_from=0), dense(48)),
+], streams=4, mult=0.4)
+TINY = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
