@@ -47,30 +47,58 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
   const int qcol = h * d, kcol = H * d + h * d, vcol = 2 * H * d + h * dv + blockIdx.x * kGlaCols;
   const int vcols = min(kGlaCols, dv - blockIdx.x * kGlaCols);
 
+  // A thread fetches the same column c of q, k and z for tokens j0, j0 + step, ...: the next batch's values are
+  // requested before the walk over this batch and kept as fetched; they are converted (and the decay worked out)
+  // when they go to shared memory, after the walk.
+  constexpr int NE = TB * DP / kGlaThreads, NV = (TB * kGlaCols + kGlaThreads - 1) / kGlaThreads;
+  constexpr int kTokStep = kGlaThreads / DP > 0 ? kGlaThreads / DP : 1;
+  static_assert(kGlaThreads % DP == 0 && NE * kTokStep == TB, "a thread's column must not change between its turns");
+  const int c_mine = tid % DP, j_mine = tid / DP;
+  const float b_mine = c_mine < d ? bias[qcol + c_mine] : 0.f;
+  T rq[NE], rk[NE], rv[NV];
+  float rz[NE];
+  auto fetch = [&](int tb) {
+    const int nt = min(TB, t1 - tb);
+#pragma unroll
+    for (int i = 0; i < NE; ++i) {
+      const int j = j_mine + i * kTokStep;
+      const bool ok = j < nt && c_mine < d;
+      const T* row = proj + (size_t)(tb + (ok ? j : 0)) * ld;
+      rq[i] = ok ? row[qcol + c_mine] : from_f32<T>(0.f);
+      rk[i] = ok ? row[kcol + c_mine] : from_f32<T>(0.f);
+      rz[i] = ok ? z[(size_t)(tb + j) * H * d + qcol + c_mine] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int idx = tid + i * kGlaThreads;
+      const int j = idx / kGlaCols, c = idx % kGlaCols;
+      rv[i] = (j < nt && c < vcols) ? proj[(size_t)(tb + j) * ld + vcol + c] : from_f32<T>(0.f);
+    }
+  };
+  auto stage = [&]() {
+#pragma unroll
+    for (int i = 0; i < NE; ++i) {
+      const int j = j_mine + i * kTokStep;
+      s_q[j][c_mine] = to_f32(rq[i]) * q_scale;
+      s_k[j][c_mine] = to_f32(rk[i]);
+      s_a[j][c_mine] = c_mine < d ? expf(log_sigmoid_f32(rz[i] + b_mine) * inv_tau) : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int idx = tid + i * kGlaThreads;
+      if (idx < TB * kGlaCols) s_v[idx / kGlaCols][idx % kGlaCols] = to_f32(rv[i]);
+    }
+  };
+  fetch(t0);
   for (int tb = t0; tb < t1; tb += TB) {
     const int nt = min(TB, t1 - tb);
+    __syncthreads();                       // the walk over the batch before is done with the staged tokens
+    stage();
     __syncthreads();
-    for (int idx = tid; idx < nt * DP; idx += kGlaThreads) {
-      const int j = idx / DP, c = idx % DP;
-      float qv = 0.f, kv = 0.f, av = 0.f;
-      if (c < d) {
-        const T* row = proj + (size_t)(tb + j) * ld;
-        qv = to_f32(row[qcol + c]) * q_scale;
-        kv = to_f32(row[kcol + c]);
-        av = expf(log_sigmoid_f32(z[(size_t)(tb + j) * H * d + qcol + c] + bias[qcol + c]) * inv_tau);
-      }
-      s_q[j][c] = qv;
-      s_k[j][c] = kv;
-      s_a[j][c] = av;
-    }
-    for (int idx = tid; idx < nt * kGlaCols; idx += kGlaThreads) {
-      const int j = idx / kGlaCols, c = idx % kGlaCols;
-      s_v[j][c] = c < vcols ? to_f32(proj[(size_t)(tb + j) * ld + vcol + c]) : 0.f;
-    }
-    __syncthreads();
-    for (int j = 0; j < nt; ++j) {
+    if (tb + TB < t1) fetch(tb + TB);
+    auto token = [&](int j) {
       const float v = s_v[j][col];
-      float acc = 0.f;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < RPL; i += 4) {
         const float4 a4 = *reinterpret_cast<const float4*>(&s_a[j][row_of(i)]);
@@ -80,15 +108,22 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
         S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * v);
         S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * v);
         S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * v);
-        acc = fmaf(q4.x, S[i], acc);
-        acc = fmaf(q4.y, S[i + 1], acc);
-        acc = fmaf(q4.z, S[i + 2], acc);
-        acc = fmaf(q4.w, S[i + 3], acc);
+        acc[0] = fmaf(q4.x, S[i], acc[0]);
+        acc[1] = fmaf(q4.y, S[i + 1], acc[1]);
+        acc[2] = fmaf(q4.z, S[i + 2], acc[2]);
+        acc[3] = fmaf(q4.w, S[i + 3], acc[3]);
       }
-      acc += __shfl_xor_sync(0xffffffffu, acc, 1);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 2);
-      acc += __shfl_xor_sync(0xffffffffu, acc, 4);
-      if (lane8 == 0 && live) out[(size_t)(tb + j) * H * dv + (size_t)h * dv + e] = acc;
+      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
+      if (lane8 == 0 && live) out[(size_t)(tb + j) * H * dv + (size_t)h * dv + e] = sum;
+    };
+    if (nt == TB) {
+#pragma unroll 4
+      for (int j = 0; j < TB; ++j) token(j);            // (unrolled: the next token's loads and products start under this one's sums)
+    } else {
+      for (int j = 0; j < nt; ++j) token(j);
     }
   }
   if (live) {

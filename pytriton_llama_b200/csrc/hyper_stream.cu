@@ -15,12 +15,34 @@ namespace ptl {
 
 constexpr int kMaxStreams = 8;
 
+// four neighbouring elements, from float32 (16 bytes) or bfloat16 (8 bytes)
+__device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
+  const float4 t = *reinterpret_cast<const float4*>(p);
+  v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+__device__ __forceinline__ void load4(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 t = *reinterpret_cast<const uint2*>(p);
+  const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+  const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+  v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+__device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  uint2 t;
+  t.x = *reinterpret_cast<const uint32_t*>(&lo);
+  t.y = *reinterpret_cast<const uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = t;
+}
+
 template <typename T, typename Y>
 __global__ void __launch_bounds__(256)
 stream_mix_norm_kernel(T* __restrict__ normed, float* __restrict__ streams, const T* __restrict__ init,
                        const Y* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ out,
                        const float* __restrict__ read, const float* __restrict__ weight, const int* __restrict__ rows,
-                       int S, int width, float eps) {
+                       int S, int width, float eps, int vec_ok) {
   extern __shared__ float u_row[];           // [width]
   __shared__ float red[33];
   __shared__ float s_mix[kMaxStreams * kMaxStreams], s_out[kMaxStreams], s_read[kMaxStreams];
@@ -38,6 +60,61 @@ stream_mix_norm_kernel(T* __restrict__ normed, float* __restrict__ streams, cons
   float* st = streams + (size_t)r * S * width;
   const bool store = rows == nullptr;
   float ss = 0.f;
+  if (vec_ok) {
+    // four neighbouring elements per thread and turn: 16-byte packets of the copies, 8 or 16 bytes of T; the loads of a
+    // turn are issued together and used afterwards
+    for (int w = threadIdx.x * 4; w < width; w += blockDim.x * 4) {
+      float old[kMaxStreams][4];
+      if (init) {
+        float v[4];
+        load4(init + (size_t)r * width + w, v);
+#pragma unroll
+        for (int s = 0; s < kMaxStreams; ++s)
+#pragma unroll
+          for (int k = 0; k < 4; ++k) old[s][k] = v[k];
+      } else {
+#pragma unroll
+        for (int s = 0; s < kMaxStreams; ++s) {
+          if (s < S) {
+            const float4 v = *reinterpret_cast<const float4*>(st + (size_t)s * width + w);
+            old[s][0] = v.x; old[s][1] = v.y; old[s][2] = v.z; old[s][3] = v.w;
+          } else {
+            old[s][0] = old[s][1] = old[s][2] = old[s][3] = 0.f;
+          }
+        }
+      }
+      float yv[4] = {0.f, 0.f, 0.f, 0.f};
+      if (y) load4(y + (size_t)r * width + w, yv);
+      float u[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int t = 0; t < kMaxStreams; ++t) {
+        if (t < S) {
+          float nw[4];
+#pragma unroll
+          for (int k = 0; k < 4; ++k) {
+            float acc;
+            if (y) {
+              acc = 0.f;
+#pragma unroll
+              for (int s = 0; s < kMaxStreams; ++s)
+                if (s < S) acc = fmaf(s_mix[s * S + t], old[s][k], acc);
+              acc = fmaf(s_out[t], yv[k], acc);
+            } else {
+              acc = old[t][k];
+            }
+            nw[k] = acc;
+            u[k] = fmaf(s_read[t], acc, u[k]);
+          }
+          if (store && (y || init)) *reinterpret_cast<float4*>(st + (size_t)t * width + w) = make_float4(nw[0], nw[1], nw[2], nw[3]);
+        }
+      }
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        u_row[w + k] = u[k];
+        ss = fmaf(u[k], u[k], ss);
+      }
+    }
+  } else
   for (int w = threadIdx.x; w < width; w += blockDim.x) {
     float old[kMaxStreams];
     if (init) {
@@ -78,6 +155,13 @@ stream_mix_norm_kernel(T* __restrict__ normed, float* __restrict__ streams, cons
   ss = block_sum(ss, red);
   const float rrms = 1.0f / sqrtf(ss / (float)width + eps);
   T* dst = normed + (size_t)m * width;
+  if (vec_ok) {
+    for (int w = threadIdx.x * 4; w < width; w += blockDim.x * 4) {
+      const float4 wv = *reinterpret_cast<const float4*>(weight + w);
+      store4(dst + w, u_row[w] * rrms * wv.x, u_row[w + 1] * rrms * wv.y, u_row[w + 2] * rrms * wv.z, u_row[w + 3] * rrms * wv.w);
+    }
+    return;
+  }
   for (int w = threadIdx.x; w < width; w += blockDim.x) dst[w] = from_f32<T>(u_row[w] * rrms * weight[w]);
 }
 
@@ -97,8 +181,10 @@ int stream_mix_norm(void* normed, float* streams, const void* init, const void* 
     PTL_REQUIRE(smem <= 200 * 1024, "stream_mix_norm: width %d is too large", width);
     if (int rc = raise_shared_memory("stream_mix_norm", stream_mix_norm_kernel<T, Y>, 200 * 1024, raised)) return rc;
   }
+  const int vec_ok = width % 4 == 0 && aligned16(streams) && aligned16(normed) && aligned16(weight) && (!init || aligned16(init)) &&
+                     (!y || aligned16(y));
   return launch_kernel("stream_mix_norm", stream_mix_norm_kernel<T, Y>, dim3(n_rows), dim3(256), smem, as_stream(stream),
-                       (T*)normed, streams, (const T*)init, (const Y*)y, mix, out, read, weight, rows, S, width, eps);
+                       (T*)normed, streams, (const T*)init, (const Y*)y, mix, out, read, weight, rows, S, width, eps, vec_ok);
 }
 
 // ------------------------------------------------------------------ gelu, tanh form

@@ -222,15 +222,20 @@ moe_grouped_kernel(OUT* __restrict__ C, int ldc, const T* __restrict__ A, const 
 
 // ------------------------------------------------------------------ grouped product on the tensor cores (bfloat16)
 // The same tiles with mma.sync m16n8k16: 4 warps, warp w owns columns 16*w .. 16*w+15 of the 32 x 64 tile (two
-// 16-row halves x two 8-column halves), operands staged through shared memory 32 values of K at a time with rows
-// padded to 40 elements so that the fragment loads of a warp fall into different banks.
+// 16-row halves x two 8-column halves).  Operands come through a ring of four stages of 64 values of K (cp.async,
+// three stages in flight: a tile of one or two rows, as in a step of single tokens, is a stream of weights and
+// nothing else); rows are padded to 72 elements so that the fragment loads of a warp fall into different banks.
+constexpr int kMmaK = 64, kMmaPitch = kMmaK + 8, kMmaStages = 4;
+constexpr int kMmaStageElems = (kMoeTile + 64) * kMmaPitch;
+constexpr int kMmaSmem = kMmaStages * kMmaStageElems * 2;
+
 template <typename OUT, bool GATED>
 __global__ void __launch_bounds__(128)
 moe_grouped_mma_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                        const int* __restrict__ tiles, const int* __restrict__ meta, int N, int K, size_t expert_stride,
                        int half) {
-  constexpr int kPitch = 40;
-  __shared__ __align__(16) __nv_bfloat16 sa[2][kMoeTile][kPitch], sb[2][64][kPitch];
+  extern __shared__ __align__(16) unsigned char moe_smem[];
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(moe_smem);
   pdl_wait();
   pdl_launch_dependents();
   const int tile = blockIdx.x;
@@ -250,17 +255,21 @@ moe_grouped_mma_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __rest
 #pragma unroll
       for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
 
-  auto stage = [&](int k0, int buf) {
-    // 32 rows x 32 k of A: 128 packets of 8; 64 rows x 32 k of W: 256 packets
-    {
-      const int rr = tid >> 2, ch = tid & 3;
-      const bool ok = rr < rows;
-      cp_async_16(smem_u32(&sa[buf][rr][ch * 8]), A + (size_t)(row0 + (ok ? rr : 0)) * K + k0 + ch * 8, ok);
+  auto stage = [&](int kb, int buf) {
+    __nv_bfloat16* sa = ring + (size_t)buf * kMmaStageElems;
+    __nv_bfloat16* sb = sa + kMoeTile * kMmaPitch;
+    const int k0 = kb * kMmaK;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                        // 32 rows x 8 packets of A
+      const int idx = tid + 128 * i;
+      const int rr = idx >> 3, ch = idx & 7;
+      const bool ok = rr < rows && k0 + ch * 8 < K;
+      cp_async_16(smem_u32(sa + rr * kMmaPitch + ch * 8), A + (size_t)(row0 + (ok ? rr : 0)) * K + (ok ? k0 + ch * 8 : 0), ok);
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {
+    for (int i = 0; i < 4; ++i) {                        // 64 rows x 8 packets of W
       const int idx = tid + 128 * i;
-      const int cc = idx >> 2, ch = idx & 3;
+      const int cc = idx >> 3, ch = idx & 7;
       int wrow;
       bool ok;
       if (GATED) {
@@ -271,45 +280,51 @@ moe_grouped_mma_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __rest
         wrow = j0 + cc;
         ok = wrow < N;
       }
-      cp_async_16(smem_u32(&sb[buf][cc][ch * 8]), Wexp + (size_t)(ok ? wrow : 0) * K + k0 + ch * 8, ok);
+      ok = ok && k0 + ch * 8 < K;
+      cp_async_16(smem_u32(sb + cc * kMmaPitch + ch * 8), Wexp + (size_t)(ok ? wrow : 0) * K + (ok ? k0 + ch * 8 : 0), ok);
     }
   };
-  const int nk = K / 32;
-  stage(0, 0);
-  cp_async_commit();
-  for (int kb = 0; kb < nk; ++kb) {
-    if (kb + 1 < nk) stage((kb + 1) * 32, (kb + 1) & 1);
-    cp_async_commit();
-    cp_async_wait<1>();
-    __syncthreads();
-    const int buf = kb & 1;
+  const int nk = (K + kMmaK - 1) / kMmaK;
 #pragma unroll
-    for (int ks = 0; ks < 2; ++ks) {
+  for (int s = 0; s < kMmaStages - 1; ++s) {
+    if (s < nk) stage(s, s);
+    cp_async_commit();
+  }
+  for (int kb = 0; kb < nk; ++kb) {
+    cp_async_wait<kMmaStages - 2>();
+    __syncthreads();                                     // stage kb has landed, and everybody is done with stage kb - 1
+    if (kb + kMmaStages - 1 < nk) stage(kb + kMmaStages - 1, (kb + kMmaStages - 1) % kMmaStages);
+    cp_async_commit();
+    const __nv_bfloat16* sa = ring + (size_t)(kb % kMmaStages) * kMmaStageElems;
+    const __nv_bfloat16* sb = sa + kMoeTile * kMmaPitch;
+#pragma unroll
+    for (int ks = 0; ks < kMmaK / 16; ++ks) {
       uint32_t bfrag[2][2];
 #pragma unroll
       for (int nt = 0; nt < 2; ++nt) {
-        const __nv_bfloat16* bp = &sb[buf][warp * 16 + nt * 8 + g][ks * 16 + 2 * c];
+        const __nv_bfloat16* bp = sb + (warp * 16 + nt * 8 + g) * kMmaPitch + ks * 16 + 2 * c;
         bfrag[nt][0] = *reinterpret_cast<const uint32_t*>(bp);
         bfrag[nt][1] = *reinterpret_cast<const uint32_t*>(bp + 8);
       }
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt) {
+        if (mt * 16 >= rows) continue;                   // (uniform over the block) a tile of few rows has no second half
         uint32_t afrag[4];
-        const __nv_bfloat16* ap = &sa[buf][mt * 16 + g][ks * 16 + 2 * c];
+        const __nv_bfloat16* ap = sa + (mt * 16 + g) * kMmaPitch + ks * 16 + 2 * c;
         afrag[0] = *reinterpret_cast<const uint32_t*>(ap);
-        afrag[1] = *reinterpret_cast<const uint32_t*>(ap + 8 * kPitch);
+        afrag[1] = *reinterpret_cast<const uint32_t*>(ap + 8 * kMmaPitch);
         afrag[2] = *reinterpret_cast<const uint32_t*>(ap + 8);
-        afrag[3] = *reinterpret_cast<const uint32_t*>(ap + 8 * kPitch + 8);
+        afrag[3] = *reinterpret_cast<const uint32_t*>(ap + 8 * kMmaPitch + 8);
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) mma_bf16_16816(acc[mt][nt], afrag, bfrag[nt][0], bfrag[nt][1]);
       }
     }
-    __syncthreads();
   }
   cp_async_wait<0>();
   if (GATED) {
     // up values go through shared memory to the warp that holds the gates of the same features
-    __shared__ float s_up[kMoeTile][33];
+    __syncthreads();                                     // the ring is free
+    float* s_up = reinterpret_cast<float*>(moe_smem);    // [32][33]
     if (warp >= 2) {
 #pragma unroll
       for (int mt = 0; mt < 2; ++mt)
@@ -317,7 +332,7 @@ moe_grouped_mma_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __rest
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
           for (int e = 0; e < 4; ++e)
-            s_up[mt * 16 + g + (e >> 1) * 8][(warp - 2) * 16 + nt * 8 + 2 * c + (e & 1)] = acc[mt][nt][e];
+            s_up[(mt * 16 + g + (e >> 1) * 8) * 33 + (warp - 2) * 16 + nt * 8 + 2 * c + (e & 1)] = acc[mt][nt][e];
     }
     __syncthreads();
     if (warp < 2) {
@@ -329,7 +344,7 @@ moe_grouped_mma_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __rest
           for (int e = 0; e < 4; ++e) {
             const int rr = mt * 16 + g + (e >> 1) * 8, cc = warp * 16 + nt * 8 + 2 * c + (e & 1);
             const int f = j0 + cc;
-            if (rr < rows && f < half) C[(size_t)(row0 + rr) * ldc + f] = from_f32<OUT>(moe_silu(acc[mt][nt][e]) * s_up[rr][cc]);
+            if (rr < rows && f < half) C[(size_t)(row0 + rr) * ldc + f] = from_f32<OUT>(moe_silu(acc[mt][nt][e]) * s_up[rr * 33 + cc]);
           }
     }
   } else {
@@ -397,12 +412,16 @@ int moe_grouped(void* C, int ldc, const void* A, const void* W, const int* tiles
   const dim3 grid(max_tiles, gated ? (half + 31) / 32 : (N + 63) / 64);
   PTL_REQUIRE(grid.y <= 65535, "moe_grouped: too many column tiles");
   if constexpr (sizeof(T) == 2) {
-    if (tensor_cores && K % 32 == 0 && aligned16(A) && aligned16(W)) {
-      if (gated)
-        return launch_kernel("moe_grouped_mma", moe_grouped_mma_kernel<T, true>, grid, dim3(128), 0, as_stream(stream), (T*)C, ldc,
-                             (const T*)A, (const T*)W, tiles, meta, N, K, stride, half);
-      return launch_kernel("moe_grouped_mma", moe_grouped_mma_kernel<float, false>, grid, dim3(128), 0, as_stream(stream), (float*)C,
-                           ldc, (const T*)A, (const T*)W, tiles, meta, N, K, stride, half);
+    if (tensor_cores && K % 8 == 0 && aligned16(A) && aligned16(W)) {
+      static SmemRaised raised_gated = {}, raised_plain = {};
+      if (gated) {
+        if (int rc = raise_shared_memory("moe_grouped_mma", moe_grouped_mma_kernel<T, true>, kMmaSmem, raised_gated)) return rc;
+        return launch_kernel("moe_grouped_mma", moe_grouped_mma_kernel<T, true>, grid, dim3(128), kMmaSmem, as_stream(stream),
+                             (T*)C, ldc, (const T*)A, (const T*)W, tiles, meta, N, K, stride, half);
+      }
+      if (int rc = raise_shared_memory("moe_grouped_mma", moe_grouped_mma_kernel<float, false>, kMmaSmem, raised_plain)) return rc;
+      return launch_kernel("moe_grouped_mma", moe_grouped_mma_kernel<float, false>, grid, dim3(128), kMmaSmem, as_stream(stream),
+                           (float*)C, ldc, (const T*)A, (const T*)W, tiles, meta, N, K, stride, half);
     }
   }
   if (gated)

@@ -124,6 +124,9 @@ __device__ __forceinline__ void wa_two_fma(float& hi, float& lo, float a, float 
   hi = t;
   lo = __fadd_rn(lo, __fadd_rn(e, r));
 }
+__device__ __forceinline__ float2 unpack_pair(uint32_t v) {
+  return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&v));
+}
 __device__ __forceinline__ void wa_two_scale(float& hi, float& lo, float c) {
   const float h = __fmul_rn(hi, c);
   lo = fmaf(lo, c, fmaf(hi, c, -h));
@@ -136,8 +139,10 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
                         const T* __restrict__ q, const T* __restrict__ cache, const int* __restrict__ block_table,
                         const int* __restrict__ tok_req, const int* __restrict__ positions, int q_stride, int out_stride,
                         int bt_stride, int H, int G, int d, int dv, int page_size, float scale, int window, int keep,
-                        int splits, int num_pages, int vec_ok, const int* __restrict__ items) {
+                        int splits, int num_pages, int vec_ok, const int* __restrict__ items, int wide_ok) {
   extern __shared__ float qs_all[];  // [warps][d]
+  __shared__ float s_pr[kWaWarps][32];
+  __shared__ unsigned long long s_vb[kWaWarps][32];
   pdl_wait();
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -185,6 +190,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
       vbase = (size_t)page * page_stride + v_plane + in_page * dv;
       float dot = 0.f, dot_lo = 0.f;
       if (vec_ok) {
+#pragma unroll 4
         for (int i = 0; i < d; i += VN) {
           Vec16<T> kv = load16(kp + i);
 #pragma unroll
@@ -217,18 +223,42 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
       for (int i = 0; i < kWaMaxPerLane; ++i) acc[i] *= alpha;
     }
     m = m_new;
+    // every lane needs every key's weight and value row: they go through shared memory, so that the walk below has
+    // neither shuffles nor branches and several keys' loads are in flight (a key that is not seen has weight 0 and the
+    // address of the cache's first value row)
+    __syncwarp();
+    s_pr[warp][lane] = pr;
+    s_vb[warp][lane] = valid ? (unsigned long long)vbase : (unsigned long long)v_plane;
+    __syncwarp();
     const int nvalid = min(32, i_end - i0);
-    for (int j = 0; j < nvalid; ++j) {
-      const float pj = __shfl_sync(0xffffffffu, pr, j);
-      const unsigned long long bj = __shfl_sync(0xffffffffu, (unsigned long long)vbase, j);
-      if (pj == 0.f) continue;   // uniform over the warp: a skipped key has no valid address
-      const T* vp = cache + (size_t)bj;
+    if (wide_ok) {
+      // value heads of 32 * CH elements, CH = 2 or 4: a lane owns CH neighbours and fetches them as one word or two
+#pragma unroll 4
+      for (int j = 0; j < nvalid; ++j) {
+        const float pj = s_pr[warp][j];
+        const T* vp = cache + (size_t)s_vb[warp][j] + lane * wide_ok;
+        if (wide_ok == 4) {
+          const uint2 raw = *reinterpret_cast<const uint2*>(vp);
+          const float2 a = unpack_pair(raw.x), b = unpack_pair(raw.y);
+          acc[0] = fmaf(pj, a.x, acc[0]); acc[1] = fmaf(pj, a.y, acc[1]);
+          acc[2] = fmaf(pj, b.x, acc[2]); acc[3] = fmaf(pj, b.y, acc[3]);
+        } else {
+          const float2 a = unpack_pair(*reinterpret_cast<const uint32_t*>(vp));
+          acc[0] = fmaf(pj, a.x, acc[0]); acc[1] = fmaf(pj, a.y, acc[1]);
+        }
+      }
+    } else {
+#pragma unroll 2
+      for (int j = 0; j < nvalid; ++j) {
+        const float pj = s_pr[warp][j];
+        const T* vp = cache + (size_t)s_vb[warp][j];
 #pragma unroll
-      for (int i = 0; i < kWaMaxPerLane; ++i) {
-        const int dd = lane + 32 * i;
-        if (dd < dv) {
-          if constexpr (kCompensated) wa_two_fma(acc[i], acc_lo[i], pj, to_f32(vp[dd]));
-          else acc[i] = fmaf(pj, to_f32(vp[dd]), acc[i]);
+        for (int i = 0; i < kWaMaxPerLane; ++i) {
+          const int dd = lane + 32 * i;
+          if (dd < dv) {
+            if constexpr (kCompensated) wa_two_fma(acc[i], acc_lo[i], pj, to_f32(vp[dd]));
+            else acc[i] = fmaf(pj, to_f32(vp[dd]), acc[i]);
+          }
         }
       }
     }
@@ -243,16 +273,16 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
     T* o = out + (size_t)t * out_stride + (size_t)h * dv;
 #pragma unroll
     for (int i = 0; i < kWaMaxPerLane; ++i) {
-      const int dd = lane + 32 * i;
-      if (dd < dv) o[dd] = from_f32<T>(acc[i] * inv);
+      const int dd = wide_ok ? lane * wide_ok + i : lane + 32 * i;
+      if (dd < dv && (!wide_ok || i < wide_ok)) o[dd] = from_f32<T>(acc[i] * inv);
     }
   } else {
     const size_t idx = ((size_t)t * H + h) * splits + split;
     float* pa = part_acc + idx * dv;
 #pragma unroll
     for (int i = 0; i < kWaMaxPerLane; ++i) {
-      const int dd = lane + 32 * i;
-      if (dd < dv) pa[dd] = acc[i];
+      const int dd = wide_ok ? lane * wide_ok + i : lane + 32 * i;
+      if (dd < dv && (!wide_ok || i < wide_ok)) pa[dd] = acc[i];
     }
     if (lane == 0) { part_ml[idx * 2] = m; part_ml[idx * 2 + 1] = l; }
   }
@@ -314,11 +344,16 @@ int window_attention(void* out, const void* q, const void* cache, const int* blo
   constexpr int VN = Vec16<T>::N;
   const int vec_ok = aligned16(cache) && d % VN == 0 && ((size_t)page_size * G * (d + dv)) % VN == 0 &&
                      ((size_t)G * page_size * d) % VN == 0;
+  // bfloat16 value heads of 64 or 128 whose rows start on 8-byte boundaries: a lane fetches 2 or 4 neighbours at once
+  int wide_ok = 0;
+  if (sizeof(T) == 2 && (dv == 64 || dv == 128) && aligned16(cache) && ((size_t)G * page_size * d) % 4 == 0 &&
+      ((size_t)page_size * G * (d + dv)) % 4 == 0)
+    wide_ok = dv / 32;
   dim3 grid(tokens, (H + kWaWarps - 1) / kWaWarps, splits);
   const size_t smem = (size_t)kWaWarps * d * sizeof(float);
   int rc = launch_kernel("window_attention", window_attention_kernel<T>, grid, dim3(kWaWarps * 32), smem, as_stream(stream),
                          (T*)out, part_acc, part_ml, (const T*)q, (const T*)cache, block_table, tok_req, positions, q_stride,
-                         out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages, vec_ok, items);
+                         out_stride, bt_stride, H, G, d, dv, page_size, scale, window, keep, splits, num_pages, vec_ok, items, wide_ok);
   if (rc) return rc;
   if (splits > 1) {
     const long long pairs = (long long)tokens * H;
