@@ -20,6 +20,7 @@
 namespace ptl {
 
 constexpr int kMoeTile = 32;          // rows of a tile
+constexpr int kMoeWide = 128;         // rows of a wide tile (steps of many tokens)
 constexpr int kMoeMaxExperts = 1024;
 
 __device__ __forceinline__ float sigmoid_f32(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -69,11 +70,12 @@ moe_route_kernel(int* __restrict__ ids, float* __restrict__ weights, const float
 }
 
 // ------------------------------------------------------------------ plan
-// tiles: [max_tiles][3] = expert, first row, rows; meta[0] = number of tiles.
+// tiles: [max_tiles][3] = expert, first row, rows; meta[0] = number of tiles.  wide: the same rows cut into tiles of up
+// to kMoeWide rows, [max_wide][3]; meta[1] = their number.
 __global__ void __launch_bounds__(1024)
 moe_plan_kernel(int* __restrict__ pos, int* __restrict__ tiles, int* __restrict__ meta, const int* __restrict__ ids, int n,
-                int E, int max_tiles) {
-  __shared__ int cnt[kMoeMaxExperts], first[kMoeMaxExperts], tile0[kMoeMaxExperts];
+                int E, int max_tiles, int* __restrict__ wide, int max_wide) {
+  __shared__ int cnt[kMoeMaxExperts], first[kMoeMaxExperts], tile0[kMoeMaxExperts], wide0[kMoeMaxExperts];
   pdl_wait();
   pdl_launch_dependents();
   const int tid = threadIdx.x;
@@ -86,20 +88,27 @@ moe_plan_kernel(int* __restrict__ pos, int* __restrict__ tiles, int* __restrict_
   __syncthreads();
   if (tid < 32) {
     // exclusive sums of the experts' tile counts, 32 experts at a time
-    int running = 0;
+    int running = 0, running_wide = 0;
     for (int e0 = 0; e0 < E; e0 += 32) {
       const int e = e0 + tid;
       const int nt = e < E ? (cnt[e] + kMoeTile - 1) / kMoeTile : 0;
-      int incl = nt;
+      const int nw = e < E ? (cnt[e] + kMoeWide - 1) / kMoeWide : 0;
+      int incl = nt, incl_w = nw;
 #pragma unroll
       for (int o = 1; o < 32; o <<= 1) {
         const int v = __shfl_up_sync(0xffffffffu, incl, o);
-        if (tid >= o) incl += v;
+        const int vw = __shfl_up_sync(0xffffffffu, incl_w, o);
+        if (tid >= o) { incl += v; incl_w += vw; }
       }
-      if (e < E) { tile0[e] = running + incl - nt; first[e] = (running + incl - nt) * kMoeTile; }
+      if (e < E) {
+        tile0[e] = running + incl - nt;
+        first[e] = (running + incl - nt) * kMoeTile;
+        wide0[e] = running_wide + incl_w - nw;
+      }
       running += __shfl_sync(0xffffffffu, incl, 31);
+      running_wide += __shfl_sync(0xffffffffu, incl_w, 31);
     }
-    if (tid == 0) meta[0] = min(running, max_tiles);
+    if (tid == 0) { meta[0] = min(running, max_tiles); meta[1] = wide ? min(running_wide, max_wide) : 0; }
   }
   __syncthreads();
   for (int e = tid; e < E; e += blockDim.x) {
@@ -110,6 +119,14 @@ moe_plan_kernel(int* __restrict__ pos, int* __restrict__ tiles, int* __restrict_
         tiles[3 * ti] = e;
         tiles[3 * ti + 1] = first[e] + r;
         tiles[3 * ti + 2] = min(kMoeTile, c - r);
+      }
+    }
+    for (int i = 0, r = 0; wide && r < c; ++i, r += kMoeWide) {
+      const int ti = wide0[e] + i;
+      if (ti < max_wide) {
+        wide[3 * ti] = e;
+        wide[3 * ti + 1] = first[e] + r;
+        wide[3 * ti + 2] = min(kMoeWide, c - r);
       }
     }
   }
@@ -360,6 +377,155 @@ moe_grouped_mma_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __rest
   }
 }
 
+// ------------------------------------------------------------------ wide tiles on the tensor cores (steps of many tokens)
+// 128 rows x 128 weight rows per block, 8 warps as 4 (rows) x 2 (columns), each 32 x 64 of the tile; fragments by
+// ldmatrix from a ring of four stages of 32 values of K whose rows are padded to 80 bytes (eight rows of a fragment
+// then start in eight different groups of four banks).  GATED: the 64 columns of a warp are 32 gate rows and the up
+// rows of the same 32 features, so a thread holds a gate and its up value in the same place of two accumulators.
+constexpr int kWideK = 32, kWidePitch = kWideK + 8, kWideStages = 4;
+constexpr int kWideStageElems = (kMoeWide + 128) * kWidePitch;
+constexpr int kWideSmem = kWideStages * kWideStageElems * 2;
+
+template <typename OUT, bool GATED>
+__global__ void __launch_bounds__(256)
+moe_grouped_wide_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                        const int* __restrict__ tiles, const int* __restrict__ meta, int N, int K, size_t expert_stride,
+                        int half) {
+  extern __shared__ __align__(16) unsigned char wide_smem[];
+  __nv_bfloat16* ring = reinterpret_cast<__nv_bfloat16*>(wide_smem);
+  pdl_wait();
+  pdl_launch_dependents();
+  const int tile = blockIdx.x;
+  if (tile >= meta[1]) return;
+  const int expert = tiles[3 * tile], row0 = tiles[3 * tile + 1], rows = tiles[3 * tile + 2];
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 1, wn = warp & 1;
+  const int g = lane >> 2, c = lane & 3;
+  const int j0 = blockIdx.y * (GATED ? 64 : 128);          // first output feature of the block
+  const __nv_bfloat16* Wexp = W + (size_t)expert * expert_stride;
+  // weight row of tile column cc (0..127)
+  auto weight_row = [&](int cc, bool& ok) {
+    if (GATED) {
+      const int f = j0 + (cc >> 6) * 32 + (cc & 31);
+      ok = f < half;
+      return ((cc & 63) < 32 ? 0 : half) + f;
+    }
+    ok = j0 + cc < N;
+    return j0 + cc;
+  };
+  float acc[2][8][4];
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) acc[mt][nt][e] = 0.f;
+
+  auto stage = [&](int kb, int buf) {
+    __nv_bfloat16* sa = ring + (size_t)buf * kWideStageElems;
+    __nv_bfloat16* sb = sa + kMoeWide * kWidePitch;
+    const int k0 = kb * kWideK;
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                        // 128 rows x 4 packets of A
+      const int idx = tid + 256 * i;
+      const int rr = idx >> 2, ch = idx & 3;
+      const bool ok = rr < rows && k0 + ch * 8 < K;
+      cp_async_16(smem_u32(sa + rr * kWidePitch + ch * 8), A + (size_t)(row0 + (ok ? rr : 0)) * K + (ok ? k0 + ch * 8 : 0), ok);
+    }
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {                        // 128 rows x 4 packets of W
+      const int idx = tid + 256 * i;
+      const int cc = idx >> 2, ch = idx & 3;
+      bool ok;
+      const int wrow = weight_row(cc, ok);
+      ok = ok && k0 + ch * 8 < K;
+      cp_async_16(smem_u32(sb + cc * kWidePitch + ch * 8), Wexp + (size_t)(ok ? wrow : 0) * K + (ok ? k0 + ch * 8 : 0), ok);
+    }
+  };
+  const int nk = (K + kWideK - 1) / kWideK;
+#pragma unroll
+  for (int s = 0; s < kWideStages - 1; ++s) {
+    if (s < nk) stage(s, s);
+    cp_async_commit();
+  }
+  const int id = lane >> 3, l7 = lane & 7;
+  for (int kb = 0; kb < nk; ++kb) {
+    cp_async_wait<kWideStages - 2>();
+    __syncthreads();
+    if (kb + kWideStages - 1 < nk) stage(kb + kWideStages - 1, (kb + kWideStages - 1) % kWideStages);
+    cp_async_commit();
+    const uint32_t sa = smem_u32(ring + (size_t)(kb % kWideStages) * kWideStageElems);
+    const uint32_t sb = sa + kMoeWide * kWidePitch * 2;
+#pragma unroll
+    for (int ks = 0; ks < kWideK / 16; ++ks) {
+      uint32_t af[2][4];
+#pragma unroll
+      for (int mt = 0; mt < 2; ++mt) {
+        const int row = wm * 32 + mt * 16 + (id & 1) * 8 + l7;
+        ldmatrix_x4(af[mt], sa + row * (kWidePitch * 2) + (2 * ks + (id >> 1)) * 16);
+      }
+#pragma unroll
+      for (int np = 0; np < 4; ++np) {
+        uint32_t bf[4];
+        const int col = wn * 64 + np * 16 + (id >> 1) * 8 + l7;
+        ldmatrix_x4(bf, sb + col * (kWidePitch * 2) + (2 * ks + (id & 1)) * 16);
+#pragma unroll
+        for (int mt = 0; mt < 2; ++mt) {
+          mma_bf16_16816(acc[mt][2 * np], af[mt], bf[0], bf[1]);
+          mma_bf16_16816(acc[mt][2 * np + 1], af[mt], bf[2], bf[3]);
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+#pragma unroll
+  for (int mt = 0; mt < 2; ++mt)
+#pragma unroll
+    for (int e2 = 0; e2 < 2; ++e2) {
+      const int rr = wm * 32 + mt * 16 + g + e2 * 8;
+      if (rr >= rows) continue;
+      OUT* dst = C + (size_t)(row0 + rr) * ldc;
+      if (GATED) {
+#pragma unroll
+        for (int nt = 0; nt < 4; ++nt)
+#pragma unroll
+          for (int e1 = 0; e1 < 2; ++e1) {
+            const int f = j0 + wn * 32 + nt * 8 + 2 * c + e1;
+            if (f < half) dst[f] = from_f32<OUT>(moe_silu(acc[mt][nt][2 * e2 + e1]) * acc[mt][nt + 4][2 * e2 + e1]);
+          }
+      } else {
+#pragma unroll
+        for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+          for (int e1 = 0; e1 < 2; ++e1) {
+            const int cc = j0 + wn * 64 + nt * 8 + 2 * c + e1;
+            if (cc < N) dst[cc] = from_f32<OUT>(acc[mt][nt][2 * e2 + e1]);
+          }
+      }
+    }
+}
+
+int moe_grouped_wide(void* C, int ldc, const void* A, const void* W, const int* wide, const int* meta, int max_wide, int N, int K,
+                     int gated, void* stream) {
+  PTL_REQUIRE(max_wide >= 0 && N > 0 && K > 0 && (!gated || N % 2 == 0), "moe_grouped_wide: bad sizes N=%d K=%d", N, K);
+  if (K % 8 != 0 || !aligned16(A) || !aligned16(W)) return -2;
+  if (max_wide == 0) return 0;
+  const int half = N / 2;
+  const size_t stride = (size_t)N * K;
+  const dim3 grid(max_wide, gated ? (half + 63) / 64 : (N + 127) / 128);
+  PTL_REQUIRE(grid.y <= 65535, "moe_grouped_wide: too many column tiles");
+  using B = __nv_bfloat16;
+  static SmemRaised raised_gated = {}, raised_plain = {};
+  if (gated) {
+    if (int rc = raise_shared_memory("moe_grouped_wide", moe_grouped_wide_kernel<B, true>, kWideSmem, raised_gated)) return rc;
+    return launch_kernel("moe_grouped_wide", moe_grouped_wide_kernel<B, true>, grid, dim3(256), kWideSmem, as_stream(stream), (B*)C,
+                         ldc, (const B*)A, (const B*)W, wide, meta, N, K, stride, half);
+  }
+  if (int rc = raise_shared_memory("moe_grouped_wide", moe_grouped_wide_kernel<float, false>, kWideSmem, raised_plain)) return rc;
+  return launch_kernel("moe_grouped_wide", moe_grouped_wide_kernel<float, false>, grid, dim3(256), kWideSmem, as_stream(stream),
+                       (float*)C, ldc, (const B*)A, (const B*)W, wide, meta, N, K, stride, half);
+}
+
 // ------------------------------------------------------------------ combine
 template <typename T>
 __global__ void __launch_bounds__(256)
@@ -388,9 +554,11 @@ int moe_route(int* ids, float* weights, const float* logits, int tokens, int E, 
                        tokens, E, top);
 }
 
-int moe_plan(int* pos, int* tiles, int* meta, const int* ids, int n, int E, int max_tiles, void* stream) {
+int moe_plan(int* pos, int* tiles, int* meta, const int* ids, int n, int E, int max_tiles, int* wide, int max_wide, void* stream) {
   PTL_REQUIRE(n >= 0 && E >= 1 && E <= kMoeMaxExperts && max_tiles >= (n + kMoeTile - 1) / kMoeTile, "moe_plan: bad sizes");
-  return launch_kernel("moe_plan", moe_plan_kernel, dim3(1), dim3(1024), 0, as_stream(stream), pos, tiles, meta, ids, n, E, max_tiles);
+  PTL_REQUIRE(!wide || max_wide >= (n + kMoeWide - 1) / kMoeWide, "moe_plan: too few wide tiles");
+  return launch_kernel("moe_plan", moe_plan_kernel, dim3(1), dim3(1024), 0, as_stream(stream), pos, tiles, meta, ids, n, E, max_tiles,
+                       wide, max_wide);
 }
 
 template <typename T>
@@ -446,8 +614,15 @@ PTL_EXPORT int ptl_moe_tile_rows() { return ptl::kMoeTile; }
 PTL_EXPORT int ptl_moe_route(int* ids, float* weights, const float* logits, int tokens, int E, int top, void* stream) {
   return ptl::moe_route(ids, weights, logits, tokens, E, top, stream);
 }
-PTL_EXPORT int ptl_moe_plan(int* pos, int* tiles, int* meta, const int* ids, int n, int E, int max_tiles, void* stream) {
-  return ptl::moe_plan(pos, tiles, meta, ids, n, E, max_tiles, stream);
+PTL_EXPORT int ptl_moe_wide_rows() { return ptl::kMoeWide; }
+PTL_EXPORT int ptl_moe_plan(int* pos, int* tiles, int* meta, const int* ids, int n, int E, int max_tiles, int* wide, int max_wide,
+                            void* stream) {
+  return ptl::moe_plan(pos, tiles, meta, ids, n, E, max_tiles, wide, max_wide, stream);
+}
+// The grouped product over the wide tiles (bfloat16, tensor cores); -2 where the sizes are not taken.
+PTL_EXPORT int ptl_moe_grouped_wide_bf16(void* C, int ldc, const void* A, const void* W, const int* wide, const int* meta,
+                                         int max_wide, int N, int K, int gated, void* stream) {
+  return ptl::moe_grouped_wide(C, ldc, A, W, wide, meta, max_wide, N, K, gated, stream);
 }
 #define PTL_MOE(SUFFIX, TYPE)                                                                                                     \
   PTL_EXPORT int ptl_moe_gather##SUFFIX(void* sorted, const void* x, const int* pos, const float* weights, int n, int top,         \

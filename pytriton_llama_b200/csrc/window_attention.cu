@@ -190,7 +190,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
       vbase = (size_t)page * page_stride + v_plane + in_page * dv;
       float dot = 0.f, dot_lo = 0.f;
       if (vec_ok) {
-#pragma unroll 4
+#pragma unroll 8
         for (int i = 0; i < d; i += VN) {
           Vec16<T> kv = load16(kp + i);
 #pragma unroll
@@ -233,7 +233,7 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
     const int nvalid = min(32, i_end - i0);
     if (wide_ok) {
       // value heads of 32 * CH elements, CH = 2 or 4: a lane owns CH neighbours and fetches them as one word or two
-#pragma unroll 4
+#pragma unroll 8
       for (int j = 0; j < nvalid; ++j) {
         const float pj = s_pr[warp][j];
         const T* vp = cache + (size_t)s_vb[warp][j] + lane * wide_ok;

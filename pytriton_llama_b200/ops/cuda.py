@@ -154,8 +154,12 @@ def load_library() -> ctypes.CDLL:
     lib.ptl_moe_tile_rows.restype = _c_int
     lib.ptl_moe_route.argtypes = [_ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
     lib.ptl_moe_route.restype = _c_int
-    lib.ptl_moe_plan.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr]
+    lib.ptl_moe_plan.argtypes = [_ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _ptr, _c_int, _ptr]
     lib.ptl_moe_plan.restype = _c_int
+    lib.ptl_moe_wide_rows.argtypes = []
+    lib.ptl_moe_wide_rows.restype = _c_int
+    lib.ptl_moe_grouped_wide_bf16.argtypes = [_ptr, _c_int, _ptr, _ptr, _ptr, _ptr, _c_int, _c_int, _c_int, _c_int, _ptr]
+    lib.ptl_moe_grouped_wide_bf16.restype = _c_int
     lib.ptl_last_error.restype = ctypes.c_char_p
     lib.ptl_set_dependent_launch.argtypes = [_c_int]
     lib.ptl_get_dependent_launch.restype = _c_int
@@ -1147,13 +1151,15 @@ class CudaOps:
         return out
 
     moe_tensor_cores = os.environ.get("PTL_MOE_TC", "1") != "0"
+    MOE_WIDE_MIN_ROWS = int(os.environ.get("PTL_MOE_WIDE_MIN", "512"))   # (token, choice) pairs from which tiles of 128 rows pay
 
     def routed_experts(self, x: torch.Tensor, logits: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, top: int,
                        scale_input: bool, shared: Optional[torch.Tensor]) -> torch.Tensor:
         """x [T, width], router logits float32 [T, E], expert weights [E, 2*inter, width] (gate rows, then up rows) and
         [E, width, inter]: every token's ``top`` experts by sigmoid(logit), weighted by that score on the expert's input
-        (``scale_input``) or output, summed, plus ``shared`` [T, width]; float32 [T, width].  Five kernels and no word
-        back to the host: route, plan (sort by expert), gather, two grouped products, combine."""
+        (``scale_input``) or output, summed, plus ``shared`` [T, width]; float32 [T, width].  Six kernels and no word
+        back to the host: route, plan (sort by expert), gather, two grouped products, combine.  The products walk tiles
+        of 32 rows of one expert; in bfloat16 steps with many tokens walk tiles of 128 rows."""
         self._want(x, "x")
         self._want(logits, "logits", torch.float32)
         self._want(w_gate_up, "expert gate/up weights", x.dtype)
@@ -1168,12 +1174,17 @@ class CudaOps:
         n = T * top
         tile = self.lib.ptl_moe_tile_rows()
         max_tiles = -(-n // tile) + min(E, n)
+        use_wide = (x.dtype == torch.bfloat16 and self.moe_tensor_cores and n >= self.MOE_WIDE_MIN_ROWS and width % 8 == 0
+                    and inter % 8 == 0)
+        max_wide = -(-n // self.lib.ptl_moe_wide_rows()) + min(E, n) if use_wide else 0
         stream = self._stream()
-        ints = self.empty((2 * n + 3 * max_tiles + 4,), torch.int32)
-        ids, pos, tiles, meta = ints[:n], ints[n:2 * n], ints[2 * n:2 * n + 3 * max_tiles], ints[2 * n + 3 * max_tiles:]
+        ints = self.empty((2 * n + 3 * max_tiles + 3 * max_wide + 4,), torch.int32)
+        ids, pos, tiles = ints[:n], ints[n:2 * n], ints[2 * n:2 * n + 3 * max_tiles]
+        wide = ints[2 * n + 3 * max_tiles:2 * n + 3 * max_tiles + 3 * max_wide] if use_wide else None
+        meta = ints[2 * n + 3 * max_tiles + 3 * max_wide:]
         weights = self.empty((n,), torch.float32)
         self._check(self.lib.ptl_moe_route(_p(ids), _p(weights), _p(logits), T, E, top, stream))
-        self._check(self.lib.ptl_moe_plan(_p(pos), _p(tiles), _p(meta), _p(ids), n, E, max_tiles, stream))
+        self._check(self.lib.ptl_moe_plan(_p(pos), _p(tiles), _p(meta), _p(ids), n, E, max_tiles, _p(wide), max_wide, stream))
         rows = max_tiles * tile
         sorted_x = self.empty((rows, width), x.dtype)
         sfx = _suffix(x.dtype)
@@ -1182,9 +1193,15 @@ class CudaOps:
         hidden = self.empty((rows, inter), x.dtype)
         tc = int(self.moe_tensor_cores)
         grouped = getattr(self.lib, "ptl_moe_grouped" + sfx)
-        self._check(grouped(_p(hidden), inter, _p(sorted_x), _p(w_gate_up), _p(tiles), _p(meta), max_tiles, two_inter, width, 1, tc, stream))
         y = self.empty((rows, width), torch.float32)
-        self._check(grouped(_p(y), width, _p(hidden), _p(w_down), _p(tiles), _p(meta), max_tiles, width, inter, 0, tc, stream))
+        if use_wide:
+            self._check(self.lib.ptl_moe_grouped_wide_bf16(_p(hidden), inter, _p(sorted_x), _p(w_gate_up), _p(wide), _p(meta), max_wide,
+                                                           two_inter, width, 1, stream))
+            self._check(self.lib.ptl_moe_grouped_wide_bf16(_p(y), width, _p(hidden), _p(w_down), _p(wide), _p(meta), max_wide, width,
+                                                           inter, 0, stream))
+        else:
+            self._check(grouped(_p(hidden), inter, _p(sorted_x), _p(w_gate_up), _p(tiles), _p(meta), max_tiles, two_inter, width, 1, tc, stream))
+            self._check(grouped(_p(y), width, _p(hidden), _p(w_down), _p(tiles), _p(meta), max_tiles, width, inter, 0, tc, stream))
         out = self.empty((T, width), torch.float32)
         self._check(getattr(self.lib, "ptl_moe_combine" + sfx)(_p(out), _p(y), _p(shared), _p(pos), _p(weights), T, top, width,
                                                                int(bool(scale_input)), stream))

@@ -222,7 +222,8 @@ def test_a_far_token_survives_hundreds_of_decays(ops):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("T,W,ff,E,top,scale_input,shared", [(45, 64, 32, 8, 2, True, True), (3, 96, 64, 16, 1, True, False),
                                                             (130, 128, 40, 5, 3, False, True), (1, 72, 24, 3, 3, True, True),
-                                                            (300, 64, 16, 2, 1, True, False), (33, 40, 8, 40, 4, True, True)])
+                                                            (300, 64, 16, 2, 1, True, False), (33, 40, 8, 40, 4, True, True),
+                                                            (700, 128, 72, 6, 2, True, True), (1100, 64, 200, 3, 1, False, False)])
 def test_routed_experts(ops, dtype, T, W, ff, E, top, scale_input, shared):
     g = torch.Generator().manual_seed(T + W + E)
     dt, ref = DTYPES[dtype], TorchOps()
@@ -230,7 +231,7 @@ def test_routed_experts(ops, dtype, T, W, ff, E, top, scale_input, shared):
     wgu, wd = _rand(g, E, 2 * ff, W, scale=W ** -0.5).to(dt), _rand(g, E, W, ff, scale=ff ** -0.5).to(dt)
     sh = _rand(g, T, W).to(dt) if shared else None
     want = ref.routed_experts(x, logits, wgu, wd, top, scale_input, sh)
-    for tc in (True, False):                                # tensor cores (bfloat16 only) and CUDA cores
+    for tc in (True, False):                                # tensor cores (bfloat16 only; tiles of 128 rows from 512 rows on) and CUDA cores
         ops.moe_tensor_cores = tc
         got = ops.routed_experts(x.cuda(), logits.cuda(), wgu.cuda(), wd.cuda(), top, scale_input, None if sh is None else sh.cuda())
         _close(got, want, dtype, f"tensor cores {tc}")
