@@ -190,13 +190,22 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
       vbase = (size_t)page * page_stride + v_plane + in_page * dv;
       float dot = 0.f, dot_lo = 0.f;
       if (vec_ok) {
-#pragma unroll 8
-        for (int i = 0; i < d; i += VN) {
-          Vec16<T> kv = load16(kp + i);
+        // four packets of the key row are requested together and used afterwards: a product right behind its load
+        // holds the warp for the load's whole latency, once per packet
+        for (int i = 0; i < d; i += 4 * VN) {
+          Vec16<T> kv[4];
 #pragma unroll
-          for (int e = 0; e < VN; ++e) {
-            if constexpr (kCompensated) wa_two_fma(dot, dot_lo, qs[i + e], kv.get(e));
-            else dot = fmaf(qs[i + e], kv.get(e), dot);
+          for (int u = 0; u < 4; ++u)
+            if (i + u * VN < d) kv[u] = load16(kp + i + u * VN);
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            if (i + u * VN < d) {
+#pragma unroll
+              for (int e = 0; e < VN; ++e) {
+                if constexpr (kCompensated) wa_two_fma(dot, dot_lo, qs[i + u * VN + e], kv[u].get(e));
+                else dot = fmaf(qs[i + u * VN + e], kv[u].get(e), dot);
+              }
+            }
           }
         }
       } else {
@@ -231,33 +240,55 @@ window_attention_kernel(T* __restrict__ out, float* __restrict__ part_acc, float
     s_vb[warp][lane] = valid ? (unsigned long long)vbase : (unsigned long long)v_plane;
     __syncwarp();
     const int nvalid = min(32, i_end - i0);
+    // (lanes past the list's end hold weight 0 and the address of a value row that exists, so the walks below take
+    // whole batches of keys: their loads are requested together and used afterwards)
     if (wide_ok) {
       // value heads of 32 * CH elements, CH = 2 or 4: a lane owns CH neighbours and fetches them as one word or two
-#pragma unroll 8
-      for (int j = 0; j < nvalid; ++j) {
-        const float pj = s_pr[warp][j];
-        const T* vp = cache + (size_t)s_vb[warp][j] + lane * wide_ok;
-        if (wide_ok == 4) {
-          const uint2 raw = *reinterpret_cast<const uint2*>(vp);
-          const float2 a = unpack_pair(raw.x), b = unpack_pair(raw.y);
-          acc[0] = fmaf(pj, a.x, acc[0]); acc[1] = fmaf(pj, a.y, acc[1]);
-          acc[2] = fmaf(pj, b.x, acc[2]); acc[3] = fmaf(pj, b.y, acc[3]);
-        } else {
-          const float2 a = unpack_pair(*reinterpret_cast<const uint32_t*>(vp));
-          acc[0] = fmaf(pj, a.x, acc[0]); acc[1] = fmaf(pj, a.y, acc[1]);
+#pragma unroll
+      for (int j0 = 0; j0 < 32; j0 += 8) {
+        if (j0 >= nvalid) break;
+        uint2 raw[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const T* vp = cache + (size_t)s_vb[warp][j0 + u] + lane * wide_ok;
+          if (wide_ok == 4) raw[u] = *reinterpret_cast<const uint2*>(vp);
+          else raw[u].x = *reinterpret_cast<const uint32_t*>(vp);
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          const float pj = s_pr[warp][j0 + u];
+          const float2 a = unpack_pair(raw[u].x);
+          acc[0] = fmaf(pj, a.x, acc[0]);
+          acc[1] = fmaf(pj, a.y, acc[1]);
+          if (wide_ok == 4) {
+            const float2 b = unpack_pair(raw[u].y);
+            acc[2] = fmaf(pj, b.x, acc[2]);
+            acc[3] = fmaf(pj, b.y, acc[3]);
+          }
         }
       }
     } else {
-#pragma unroll 2
-      for (int j = 0; j < nvalid; ++j) {
-        const float pj = s_pr[warp][j];
-        const T* vp = cache + (size_t)s_vb[warp][j];
+      for (int j0 = 0; j0 < nvalid; j0 += 4) {
+        T raw[4][kWaMaxPerLane];
 #pragma unroll
-        for (int i = 0; i < kWaMaxPerLane; ++i) {
-          const int dd = lane + 32 * i;
-          if (dd < dv) {
-            if constexpr (kCompensated) wa_two_fma(acc[i], acc_lo[i], pj, to_f32(vp[dd]));
-            else acc[i] = fmaf(pj, to_f32(vp[dd]), acc[i]);
+        for (int u = 0; u < 4; ++u) {
+          const T* vp = cache + (size_t)s_vb[warp][j0 + u];
+#pragma unroll
+          for (int i = 0; i < kWaMaxPerLane; ++i) {
+            const int dd = lane + 32 * i;
+            if (dd < dv) raw[u][i] = vp[dd];
+          }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const float pj = s_pr[warp][j0 + u];
+#pragma unroll
+          for (int i = 0; i < kWaMaxPerLane; ++i) {
+            const int dd = lane + 32 * i;
+            if (dd < dv) {
+              if constexpr (kCompensated) wa_two_fma(acc[i], acc_lo[i], pj, to_f32(raw[u][i]));
+              else acc[i] = fmaf(pj, to_f32(raw[u][i]), acc[i]);
+            }
           }
         }
       }
@@ -301,24 +332,51 @@ window_attention_merge_kernel(T* __restrict__ out, const float* __restrict__ par
   const int t = items ? items[pair / H] : (int)(pair / H);
   const int h = (int)(pair % H);
   const size_t idx0 = ((size_t)t * H + h) * splits;
+  // lane z holds the (maximum, sum) of part z, 32 parts at a time; the weights are handed round by shuffles and the
+  // parts' accumulators are fetched four at a time
   float M = -INFINITY;
-  for (int z = 0; z < splits; ++z) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
+  for (int z = lane; z < splits; z += 32) M = fmaxf(M, part_ml[(idx0 + z) * 2]);
+  M = warp_max(M);
   float L = 0.f;
   float acc[kWaMaxPerLane];
 #pragma unroll
   for (int i = 0; i < kWaMaxPerLane; ++i) acc[i] = 0.f;
-  for (int z = 0; z < splits; ++z) {
-    const float mz = part_ml[(idx0 + z) * 2];
-    if (!(mz > -INFINITY)) continue;
-    const float wz = expf(mz - M);
-    L = fmaf(wz, part_ml[(idx0 + z) * 2 + 1], L);
-    const float* pa = part_acc + (idx0 + z) * dv;
+  for (int z0 = 0; z0 < splits; z0 += 32) {
+    const int z = z0 + lane;
+    float wz = 0.f;
+    if (z < splits) {
+      const float mz = part_ml[(idx0 + z) * 2];
+      if (mz > -INFINITY) {
+        wz = expf(mz - M);
+        L = fmaf(wz, part_ml[(idx0 + z) * 2 + 1], L);
+      }
+    }
+    const int n = min(32, splits - z0);
+    for (int j0 = 0; j0 < n; j0 += 4) {
+      float raw[4][kWaMaxPerLane];
 #pragma unroll
-    for (int i = 0; i < kWaMaxPerLane; ++i) {
-      const int dd = lane + 32 * i;
-      if (dd < dv) acc[i] = fmaf(wz, pa[dd], acc[i]);
+      for (int u = 0; u < 4; ++u) {
+        const float* pa = part_acc + (idx0 + z0 + min(j0 + u, n - 1)) * dv;     // an empty part wrote zeros
+#pragma unroll
+        for (int i = 0; i < kWaMaxPerLane; ++i) {
+          const int dd = lane + 32 * i;
+          if (dd < dv) raw[u][i] = pa[dd];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const float wj = __shfl_sync(0xffffffffu, wz, min(j0 + u, 31));
+        if (j0 + u < n) {
+#pragma unroll
+          for (int i = 0; i < kWaMaxPerLane; ++i) {
+            const int dd = lane + 32 * i;
+            if (dd < dv) acc[i] = fmaf(wj, raw[u][i], acc[i]);
+          }
+        }
+      }
     }
   }
+  L = warp_sum(L);
   const float inv = L > 0.f ? 1.0f / L : 0.f;
   T* o = out + (size_t)t * out_stride + (size_t)h * dv;
 #pragma unroll
