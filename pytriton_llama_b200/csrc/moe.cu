@@ -379,10 +379,11 @@ moe_grouped_mma_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __rest
 
 // ------------------------------------------------------------------ wide tiles on the tensor cores (steps of many tokens)
 // 128 rows x 128 weight rows per block, 8 warps as 4 (rows) x 2 (columns), each 32 x 64 of the tile; fragments by
-// ldmatrix from a ring of four stages of 32 values of K whose rows are padded to 80 bytes (eight rows of a fragment
-// then start in eight different groups of four banks).  GATED: the 64 columns of a warp are 32 gate rows and the up
+// ldmatrix from a ring of three stages of 64 values of K whose rows are padded to 144 bytes (eight rows of a fragment
+// then start in eight different groups of four banks); two blocks fit an SM.  GATED: the 64 columns of a warp are 32 gate rows and the up
 // rows of the same 32 features, so a thread holds a gate and its up value in the same place of two accumulators.
-constexpr int kWideK = 32, kWidePitch = kWideK + 8, kWideStages = 4;
+constexpr int kWideK = 64, kWidePitch = kWideK + 8, kWideStages = 3;
+constexpr int kWidePackets = kWideK / 8;          // 16-byte packets of a staged row
 constexpr int kWideStageElems = (kMoeWide + 128) * kWidePitch;
 constexpr int kWideSmem = kWideStages * kWideStageElems * 2;
 
@@ -426,16 +427,16 @@ moe_grouped_wide_kernel(OUT* __restrict__ C, int ldc, const __nv_bfloat16* __res
     __nv_bfloat16* sb = sa + kMoeWide * kWidePitch;
     const int k0 = kb * kWideK;
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {                        // 128 rows x 4 packets of A
+    for (int i = 0; i < kMoeWide * kWidePackets / 256; ++i) {       // 128 rows of A
       const int idx = tid + 256 * i;
-      const int rr = idx >> 2, ch = idx & 3;
+      const int rr = idx / kWidePackets, ch = idx % kWidePackets;
       const bool ok = rr < rows && k0 + ch * 8 < K;
       cp_async_16(smem_u32(sa + rr * kWidePitch + ch * 8), A + (size_t)(row0 + (ok ? rr : 0)) * K + (ok ? k0 + ch * 8 : 0), ok);
     }
 #pragma unroll
-    for (int i = 0; i < 2; ++i) {                        // 128 rows x 4 packets of W
+    for (int i = 0; i < 128 * kWidePackets / 256; ++i) {            // 128 rows of W
       const int idx = tid + 256 * i;
-      const int cc = idx >> 2, ch = idx & 3;
+      const int cc = idx / kWidePackets, ch = idx % kWidePackets;
       bool ok;
       const int wrow = weight_row(cc, ok);
       ok = ok && k0 + ch * 8 < K;

@@ -29,14 +29,91 @@ __global__ void __launch_bounds__(256)
 qk_norm_rotate_store_kernel(T* __restrict__ proj, int ld, int H, int G, int d, int dv, const float* __restrict__ wq,
                             const float* __restrict__ wk, float eps, const int* __restrict__ positions,
                             const float* __restrict__ freq, int dims, float amplitude, const int* __restrict__ slots,
-                            T* __restrict__ cache, int page_size, long long num_slots) {
+                            T* __restrict__ cache, int page_size, long long num_slots, int vec_ok) {
   __shared__ float red[33];
+  __shared__ float s_cs[256], s_sn[256];          // cos and sin (times the amplitude) of the token's angles, vec_ok only
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
   T* row = proj + (size_t)t * ld;
   const int nq = H * d, nk = G * d, nv = G * dv;
   float rq = 1.f, rk = 1.f;
+  constexpr int VN = Vec16<T>::N;
+  if (vec_ok) {
+    // Packets of 16 bytes: the sums of squares, then every packet of q and k (it lies within one head) normed, turned
+    // by angles worked out once per token, written back and, for k, stored; v is copied packet by packet.
+    const float pos = (float)positions[t];
+    if (freq && threadIdx.x < dims / 2) {
+      float sn, cs;
+      sincosf(pos * freq[threadIdx.x], &sn, &cs);
+      s_cs[threadIdx.x] = cs * amplitude;
+      s_sn[threadIdx.x] = sn * amplitude;
+    }
+    float sq = 0.f, sk = 0.f;
+    if (eps > 0.f) {
+      for (int i = threadIdx.x * VN; i < nq + nk; i += blockDim.x * VN) {
+        const Vec16<T> v = load16(row + i);
+        float part = 0.f;
+#pragma unroll
+        for (int e = 0; e < VN; ++e) part = fmaf(v.get(e), v.get(e), part);
+        if (i < nq) sq += part; else sk += part;
+      }
+      sq = block_sum(sq, red);
+      rq = 1.0f / sqrtf(sq / (float)nq + eps);
+      if (nk > 0) {
+        sk = block_sum(sk, red);
+        rk = 1.0f / sqrtf(sk / (float)nk + eps);
+      }
+    } else {
+      __syncthreads();
+    }
+    long long slot = (slots && cache) ? (long long)slots[t] : -1;
+    if (slot >= num_slots) slot = -1;
+    const size_t page_stride = (size_t)G * page_size * (d + dv);
+    const size_t page = slot >= 0 ? (size_t)(slot / page_size) : 0, off = slot >= 0 ? (size_t)(slot % page_size) : 0;
+    for (int i = threadIdx.x * VN; i < nq + nk; i += blockDim.x * VN) {
+      const bool is_k = i >= nq;
+      const int within = (is_k ? i - nq : i) % d;          // first entry of the packet within its head
+      const float r = is_k ? rk : rq;
+      Vec16<T> v = load16(row + i);
+      float x[VN];
+#pragma unroll
+      for (int e = 0; e < VN; ++e) x[e] = v.get(e) * r;
+      if (eps > 0.f) {
+        const float* w = is_k ? wk + (i - nq) : wq + i;
+#pragma unroll
+        for (int e = 0; e < VN; ++e) x[e] *= w[e];
+      }
+      if (freq && within < dims) {
+#pragma unroll
+        for (int e = 0; e < VN; e += 2) {
+          if (within + e + 1 < dims) {
+            const int pair = (within + e) >> 1;
+            float o1, o2;
+            rope_rotate(x[e], x[e + 1], s_cs[pair], s_sn[pair], o1, o2);
+            x[e] = o1;
+            x[e + 1] = o2;
+          }
+        }
+      }
+#pragma unroll
+      for (int e = 0; e < VN; ++e) v.set(e, x[e]);
+      store16(row + i, v);
+      if (is_k && slot >= 0) {
+        const int g = (i - nq) / d;
+        store16(cache + page * page_stride + ((size_t)g * page_size + off) * d + within, v);
+      }
+    }
+    if (slot >= 0) {
+      const T* vsrc = row + nq + nk;
+      T* vdst = cache + page * page_stride + (size_t)G * page_size * d + off * dv;
+      for (int i = threadIdx.x * VN; i < nv; i += blockDim.x * VN) {
+        const int g = i / dv, e = i % dv;
+        store16(vdst + (size_t)g * page_size * dv + e, load16(vsrc + i));
+      }
+    }
+    return;
+  }
   if (eps > 0.f) {
     float sq = 0.f, sk = 0.f;
     for (int i = threadIdx.x; i < nq; i += blockDim.x) { const float v = to_f32(row[i]); sq = fmaf(v, v, sq); }
@@ -106,9 +183,12 @@ int qk_norm_rotate_store(void* proj, int tokens, int ld, int H, int G, int d, in
   PTL_REQUIRE(eps <= 0.f || (wq && (G == 0 || wk)), "qk_norm_rotate_store: the norm needs its weights");
   PTL_REQUIRE(dims >= 0 && dims % 2 == 0 && dims <= d && (dims == 0 || freq), "qk_norm_rotate_store: rotary width %d of head size %d", dims, d);
   if (tokens == 0) return 0;
+  constexpr int VN = Vec16<T>::N;
+  const int vec_ok = d % VN == 0 && dv % VN == 0 && ld % VN == 0 && dims <= 512 && aligned16(proj) &&
+                     (!cache || aligned16(cache)) && (eps <= 0.f || (aligned16(wq) && (G == 0 || aligned16(wk))));
   return launch_kernel("qk_norm_rotate_store", qk_norm_rotate_store_kernel<T>, dim3(tokens), dim3(256), 0, as_stream(stream),
                        (T*)proj, ld, H, G, d, dv, wq, wk, eps, positions, dims > 0 ? freq : nullptr, dims, amplitude,
-                       G > 0 ? slots : nullptr, (T*)cache, page_size, num_slots);
+                       G > 0 ? slots : nullptr, (T*)cache, page_size, num_slots, vec_ok);
 }
 
 // ------------------------------------------------------------------ attention
