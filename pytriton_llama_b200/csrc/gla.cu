@@ -3,17 +3,22 @@
 //
 // proj is the projection's output [T, q | k | v | ...] (H heads of d, d, dv), z float32 [T, H*d] before
 // the bias.  A block owns 32 columns of one head's state for one request and walks the request's
-// tokens of this step in order; 8 lanes share a column, each with every eighth packet of four of the d rows
-// in registers.  Tokens come through shared memory in batches (q scaled, decay worked out while
-// staging).  The state of a request is read from its slot unless the portion starts at position 0
-// and written back at the end.  Everything after the loads is float32; a token's result does not
-// depend on how the request was cut into steps or on what else the step holds.
+// tokens of this step in order.  The 32 lanes of a warp are the 32 columns; each of the 8 warps holds
+// every eighth packet of four of the d rows in registers, so the q, k and decay values a warp needs
+// are the same for all its lanes: one shared-memory wavefront per packet.  (With 8 lanes per column
+// and the rows spread over the lanes the kernel was bound by shared-memory bandwidth, 437 wavefronts a
+// token.)  Nothing in the walk waits on a shuffle; the warps' partial read-outs of a batch meet in
+// shared memory.  Tokens come through shared memory in batches (q scaled, decay worked out while
+// staging; the next batch's values are requested before the walk over this one).  The state of a
+// request is read from its slot unless the portion starts at position 0 and written back at the end.
+// Everything after the loads is float32; a token's result does not depend on how the request was cut
+// into steps or on what else the step holds.
 #include "common.cuh"
 
 namespace ptl {
 
 constexpr int kGlaCols = 32;      // columns of the state per block
-constexpr int kGlaLanes = 8;      // lanes per column
+constexpr int kGlaLanes = 8;      // threads per column (one in each warp)
 constexpr int kGlaThreads = kGlaCols * kGlaLanes;
 
 __device__ __forceinline__ float log_sigmoid_f32(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
@@ -26,6 +31,7 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
   constexpr int DP = kGlaLanes * RPL;
   __shared__ __align__(16) float s_q[TB][DP], s_k[TB][DP], s_a[TB][DP];
   __shared__ float s_v[TB][kGlaCols];
+  __shared__ float s_part[TB][kGlaLanes][kGlaCols];        // a warp's part of a token's read-out, per column
   pdl_wait();
   pdl_launch_dependents();
   const int r = blockIdx.z, h = blockIdx.y;
@@ -33,11 +39,10 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
   const int slot = state_slot[r];
   if (t1 <= t0 || slot < 0) return;
   const int tid = threadIdx.x;
-  const int col = tid / kGlaLanes, lane8 = tid % kGlaLanes;
+  const int col = tid & 31, lane8 = tid >> 5;              // column = lane; lane8: which eighth of the rows = the warp
   const int e = blockIdx.x * kGlaCols + col;
   const bool live = e < dv;
-  // rows of this lane: packets of four, packet m of the lane being packet m * 8 + lane8 of the column, so that
-  // the eight lanes of a column read 128 consecutive bytes of a staged token
+  // rows of this warp: packets of four, packet m of the warp being packet m * 8 + lane8 of the column
   auto row_of = [&](int i) { return ((i >> 2) * kGlaLanes + lane8) * 4 + (i & 3); };
   float* st = state + (((size_t)slot * H + h) * d) * dv;
   float S[RPL];
@@ -113,17 +118,22 @@ gla_scan_kernel(float* __restrict__ out, const T* __restrict__ proj, int ld, con
         acc[2] = fmaf(q4.z, S[i + 2], acc[2]);
         acc[3] = fmaf(q4.w, S[i + 3], acc[3]);
       }
-      float sum = (acc[0] + acc[1]) + (acc[2] + acc[3]);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 1);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 2);
-      sum += __shfl_xor_sync(0xffffffffu, sum, 4);
-      if (lane8 == 0 && live) out[(size_t)(tb + j) * H * dv + (size_t)h * dv + e] = sum;
+      s_part[j][lane8][col] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
     };
     if (nt == TB) {
 #pragma unroll 4
       for (int j = 0; j < TB; ++j) token(j);            // (unrolled: the next token's loads and products start under this one's sums)
     } else {
       for (int j = 0; j < nt; ++j) token(j);
+    }
+    __syncthreads();
+    // the warps' parts of every read-out of the batch, added in the order of the warps
+    for (int idx = tid; idx < nt * kGlaCols; idx += kGlaThreads) {
+      const int j = idx / kGlaCols, c = idx % kGlaCols;
+      float sum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kGlaLanes; ++w) sum += s_part[j][w][c];
+      if (c < vcols) out[(size_t)(tb + j) * H * dv + (size_t)h * dv + blockIdx.x * kGlaCols + c] = sum;
     }
   }
   if (live) {

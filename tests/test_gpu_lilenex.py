@@ -202,6 +202,18 @@ def test_gla_walk_and_its_state(ops, dtype, H, d, dv):
     _close(Sc[2], Sb[2], "float32", "state after two portions")
 
 
+def test_strong_decays_neither_overflow_nor_leak(ops):
+    """Decays near zero (sigmoid(-30)^(1/1)): the state forgets at once and nothing becomes infinite."""
+    H, d, dv, T = 2, 32, 32, 50
+    g = torch.Generator().manual_seed(3)
+    proj, z, b = _rand(g, T, 2 * H * d + 2 * H * dv), _rand(g, T, H * d) * 10 - 20, torch.zeros(H * d)
+    Sa, Sb = torch.zeros(1, H, d, dv).cuda(), torch.zeros(1, H, d, dv)
+    oa = ops.gla_scan(proj.cuda(), z.cuda(), b.cuda(), 1.0, Sa, _ctx([T], [0], [0], "cuda:0"), H, d, dv, d ** -0.5)
+    ob = TorchOps().gla_scan(proj, z, b, 1.0, Sb, _ctx([T], [0], [0], "cpu"), H, d, dv, d ** -0.5)
+    _close(oa, ob, "float32", "read-outs")
+    _close(Sa, Sb, "float32", "state")
+
+
 def test_a_far_token_survives_hundreds_of_decays(ops):
     """Decays close to one: what was written at the first token is still read 600 tokens later, in float32."""
     H, d, dv, T = 1, 16, 16, 600
