@@ -5,7 +5,7 @@ q = W_q h, k = W_k h, v = W_v h.  With ``qk_norm_eps`` > 0 the whole query proje
 once) and the whole key projection are divided by their root mean square and multiplied by a weight
 of their own size.  The nested ``position`` part then turns neighbouring pairs of every head
 (``rotary_pairs``) or leaves them alone (``none``).  Query i sees key j <= i if i - j < ``window``
-or j < ``keep_first`` (``window`` 0: every j <= i); kept keys have their true positions.
+or j < ``keep_first`` (``window`` 0: every j <= i); a kept key was rotated by its own position like any other.
 score = (q . k) * scale, softmax, heads of ``value_dim`` concatenated, W_o.
 
 With ``own_kv`` False the layer has no key and value tensors: it attends, with its own queries and

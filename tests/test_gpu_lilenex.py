@@ -315,7 +315,7 @@ WIDE = plain.config(300, 128, [
     plain.layer("gla", plain.gla(2, 64, 64, 8.0), plain.moe(64, 6, 2, shared=64)),
     plain.layer("attention", plain.attention(4, 2, 64, 64, 0.125, size=70, keep_first=2, rot=plain.rotation(32, 10000.0, (4.0, 64, 16.0, 1.0)), kv_from=0), plain.moe(32, 4, 1)),
     plain.layer("attention", plain.attention(2, 1, 128, 128, 0.09, size=33, keep_first=0), plain.dense(64)),
-], streams=3, mult=0.5)
+], streams=2, mult=0.6)
 
 
 def _config(name):
