@@ -143,7 +143,7 @@ moe_plan_kernel(int* __restrict__ pos, int* __restrict__ tiles, int* __restrict_
 template <typename T>
 __global__ void __launch_bounds__(128)
 moe_gather_kernel(T* __restrict__ sorted, const T* __restrict__ x, const int* __restrict__ pos, const float* __restrict__ weights,
-                  int top, int width, int scale_input) {
+                  int top, int width, int scale_input, int vec_ok) {
   pdl_wait();
   pdl_launch_dependents();
   const int a = blockIdx.x;
@@ -152,6 +152,18 @@ moe_gather_kernel(T* __restrict__ sorted, const T* __restrict__ x, const int* __
   const float w = scale_input ? weights[a] : 1.f;
   const T* src = x + (size_t)(a / top) * width;
   T* dst = sorted + (size_t)row * width;
+  if (vec_ok) {
+    constexpr int VN = Vec16<T>::N;
+    for (int i = threadIdx.x * VN; i < width; i += blockDim.x * VN) {
+      Vec16<T> v = load16(src + i);
+      if (scale_input) {
+#pragma unroll
+        for (int e = 0; e < VN; ++e) v.set(e, v.get(e) * w);
+      }
+      store16(dst + i, v);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = scale_input ? from_f32<T>(to_f32(src[i]) * w) : src[i];
 }
 
@@ -531,10 +543,42 @@ int moe_grouped_wide(void* C, int ldc, const void* A, const void* W, const int* 
 template <typename T>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(float* __restrict__ out, const float* __restrict__ C, const T* __restrict__ shared_out,
-                   const int* __restrict__ pos, const float* __restrict__ weights, int top, int width, int scale_input) {
+                   const int* __restrict__ pos, const float* __restrict__ weights, int top, int width, int scale_input,
+                   int vec_ok) {
   pdl_wait();
   pdl_launch_dependents();
   const int t = blockIdx.x;
+  if (vec_ok) {
+    // four neighbours per thread and turn; the choices' rows are requested together, then added in the order of the choices
+    for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (shared_out) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) acc[e] = to_f32(shared_out[(size_t)t * width + i + e]);
+      }
+      for (int k0 = 0; k0 < top; k0 += 4) {
+        float4 v[4];
+        float wk[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int row = k0 + u < top ? pos[(size_t)t * top + k0 + u] : -1;
+          wk[u] = row < 0 ? 0.f : (scale_input ? 1.f : weights[(size_t)t * top + k0 + u]);
+          v[u] = row < 0 ? make_float4(0.f, 0.f, 0.f, 0.f) : *reinterpret_cast<const float4*>(C + (size_t)row * width + i);
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          if (scale_input) {
+            acc[0] += v[u].x; acc[1] += v[u].y; acc[2] += v[u].z; acc[3] += v[u].w;
+          } else {
+            acc[0] = fmaf(wk[u], v[u].x, acc[0]); acc[1] = fmaf(wk[u], v[u].y, acc[1]);
+            acc[2] = fmaf(wk[u], v[u].z, acc[2]); acc[3] = fmaf(wk[u], v[u].w, acc[3]);
+          }
+        }
+      }
+      *reinterpret_cast<float4*>(out + (size_t)t * width + i) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < width; i += blockDim.x) {
     float acc = shared_out ? to_f32(shared_out[(size_t)t * width + i]) : 0.f;
     for (int k = 0; k < top; ++k) {
@@ -567,8 +611,9 @@ int moe_gather(void* sorted, const void* x, const int* pos, const float* weights
                void* stream) {
   PTL_REQUIRE(n >= 0 && top >= 1 && width > 0, "moe_gather: bad sizes");
   if (n == 0) return 0;
+  const int vec_ok = width % Vec16<T>::N == 0 && aligned16(sorted) && aligned16(x);
   return launch_kernel("moe_gather", moe_gather_kernel<T>, dim3(n), dim3(128), 0, as_stream(stream), (T*)sorted, (const T*)x, pos,
-                       weights, top, width, scale_input);
+                       weights, top, width, scale_input, vec_ok);
 }
 
 template <typename T>
@@ -605,8 +650,9 @@ int moe_combine(float* out, const float* C, const void* shared_out, const int* p
                 int width, int scale_input, void* stream) {
   PTL_REQUIRE(tokens >= 0 && top >= 1 && width > 0, "moe_combine: bad sizes");
   if (tokens == 0) return 0;
+  const int vec_ok = width % 4 == 0 && aligned16(out) && aligned16(C);
   return launch_kernel("moe_combine", moe_combine_kernel<T>, dim3(tokens), dim3(256), 0, as_stream(stream), out, C,
-                       (const T*)shared_out, pos, weights, top, width, scale_input);
+                       (const T*)shared_out, pos, weights, top, width, scale_input, vec_ok);
 }
 
 }  // namespace ptl

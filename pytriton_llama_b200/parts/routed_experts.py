@@ -51,13 +51,23 @@ class RoutedExperts(Part):
         self.w_gate_up = self._to_compute(torch.stack([torch.cat([t[f"e{i}.gate"], t[f"e{i}.up"]], dim=0) for i in E]))
         self.w_down = self._to_compute(torch.stack([t[f"e{i}.down"] for i in E]))
         if self.shared_inter:
-            self.w_shared_gate_up = self._to_compute(torch.cat([t["shared.gate"], t["shared.up"]], dim=0))
+            # the shared expert is a dense gated feed-forward: where the operator set's product applies silu(gate) * up
+            # in its epilogue, gate and up rows alternate (as in parts/swiglu.py)
+            ops = self.rt.ops
+            self.alternating = bool(ops is not None and hasattr(ops, "fused_ffn_layout")
+                                    and ops.fused_ffn_layout(self.rt.dtype, self.hidden, self.shared_inter))
+            if self.alternating:
+                gu = torch.stack([t["shared.gate"], t["shared.up"]], dim=1).reshape(2 * self.shared_inter, self.hidden)
+            else:
+                gu = torch.cat([t["shared.gate"], t["shared.up"]], dim=0)
+            self.w_shared_gate_up = self._to_compute(gu)
             self.w_shared_down = self._to_compute(t["shared.down"])
 
     def forward(self, x):
         ops = self.rt.ops
         shared = None
         if self.shared_inter:
-            shared = ops.linear(ops.silu_mul(ops.linear(x, self.w_shared_gate_up)), self.w_shared_down)
+            inner = ops.gate_up_silu(x, self.w_shared_gate_up) if self.alternating else ops.silu_mul(ops.linear(x, self.w_shared_gate_up))
+            shared = ops.linear(inner, self.w_shared_down)
         logits = ops.linear(x, self.w_router, out_dtype=torch.float32)
         return ops.routed_experts(x, logits, self.w_gate_up, self.w_down, self.top, self.scale_input, shared)

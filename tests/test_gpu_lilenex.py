@@ -466,7 +466,7 @@ def test_greedy_generation_through_the_scheduler(folders, dtype):
             assert row[tok] >= row.max() - slack, (i, tok, int(row.argmax()))
 
 
-def test_trace_runner(folders, tmp_path):
+def test_trace_runner_and_command_line(folders, tmp_path):
     folder = folders("WIDE", "bfloat16", WIDE)
     seqs = {"a": random_tokens(90, 300, 1), "b": random_tokens(13, 300, 2)}
     steps = traces.mixed(seqs)
@@ -491,3 +491,9 @@ def test_trace_runner(folders, tmp_path):
                     at += 1
                 fed[e["id"]] += len(e["tokens"])
         _assert_logits(torch.stack(got), torch.stack(want), dtype, f"{dtype} replay")
+    import sys
+    proc = subprocess.run([sys.executable, str(ROOT / "cli.py"), "--checkpoints_dir", str(folder), "--temperature", "0",
+                           "--max_gen_len", "5", "--max_seq_len", "64", "--page_size", "16", "--prompt_ids", "3", "1", "4", "1", "5"],
+                          capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert len(proc.stdout.split()) == 5
