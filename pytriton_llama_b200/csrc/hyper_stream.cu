@@ -13,7 +13,7 @@
 
 namespace ptl {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMostStreams = 16;   // the kernel is compiled for up to 4, 8 and 16 copies
 
 // four neighbouring elements, from float32 (16 bytes) or bfloat16 (8 bytes)
 __device__ __forceinline__ void load4(const float* p, float (&v)[4]) {
@@ -37,7 +37,7 @@ __device__ __forceinline__ void store4(__nv_bfloat16* p, float a, float b, float
   *reinterpret_cast<uint2*>(p) = t;
 }
 
-template <typename T, typename Y>
+template <typename T, typename Y, int kMaxStreams>
 __global__ void __launch_bounds__(256)
 stream_mix_norm_kernel(T* __restrict__ normed, float* __restrict__ streams, const T* __restrict__ init,
                        const Y* __restrict__ y, const float* __restrict__ mix, const float* __restrict__ out,
@@ -170,21 +170,27 @@ int stream_mix_norm(void* normed, float* streams, const void* init, const void* 
                     const float* read, const float* weight, const int* rows, int n_rows, int S, int width, float eps,
                     void* stream) {
   PTL_REQUIRE(n_rows >= 0 && width > 0 && eps > 0.f, "stream_mix_norm: bad sizes rows=%d width=%d", n_rows, width);
-  PTL_REQUIRE(S >= 1 && S <= kMaxStreams, "stream_mix_norm: %d copies of the stream, at most %d", S, kMaxStreams);
+  PTL_REQUIRE(S >= 1 && S <= kMostStreams, "stream_mix_norm: %d copies of the stream, at most %d", S, kMostStreams);
   PTL_REQUIRE(streams && read && weight && normed, "stream_mix_norm: missing tensor");
   PTL_REQUIRE(!y || (mix && out), "stream_mix_norm: an output to write needs its mixing matrix and output vector");
   PTL_REQUIRE(!(init && y), "stream_mix_norm: the copies start from the embedding output or take a write, not both");
   if (n_rows == 0) return 0;
   const size_t smem = (size_t)width * sizeof(float);
-  static SmemRaised raised = {};
-  if (smem > 48 * 1024) {
-    PTL_REQUIRE(smem <= 200 * 1024, "stream_mix_norm: width %d is too large", width);
-    if (int rc = raise_shared_memory("stream_mix_norm", stream_mix_norm_kernel<T, Y>, 200 * 1024, raised)) return rc;
-  }
+  PTL_REQUIRE(smem <= 200 * 1024, "stream_mix_norm: width %d is too large", width);
   const int vec_ok = width % 4 == 0 && aligned16(streams) && aligned16(normed) && aligned16(weight) && (!init || aligned16(init)) &&
                      (!y || aligned16(y));
-  return launch_kernel("stream_mix_norm", stream_mix_norm_kernel<T, Y>, dim3(n_rows), dim3(256), smem, as_stream(stream),
-                       (T*)normed, streams, (const T*)init, (const Y*)y, mix, out, read, weight, rows, S, width, eps, vec_ok);
+#define PTL_STREAM_LAUNCH(MS)                                                                                                  \
+  {                                                                                                                            \
+    static SmemRaised raised = {};                                                                                             \
+    if (smem > 48 * 1024)                                                                                                      \
+      if (int rc = raise_shared_memory("stream_mix_norm", stream_mix_norm_kernel<T, Y, MS>, 200 * 1024, raised)) return rc;   \
+    return launch_kernel("stream_mix_norm", stream_mix_norm_kernel<T, Y, MS>, dim3(n_rows), dim3(256), smem, as_stream(stream), \
+                         (T*)normed, streams, (const T*)init, (const Y*)y, mix, out, read, weight, rows, S, width, eps, vec_ok); \
+  }
+  if (S <= 4) PTL_STREAM_LAUNCH(4)
+  if (S <= 8) PTL_STREAM_LAUNCH(8)
+  PTL_STREAM_LAUNCH(16)
+#undef PTL_STREAM_LAUNCH
 }
 
 // ------------------------------------------------------------------ gelu, tanh form

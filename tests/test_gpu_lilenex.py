@@ -51,7 +51,7 @@ def _rand(gen, *shape, scale=1.0):
 
 # ---------------------------------------------------------------------------- the copies of the stream
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("S,width", [(1, 40), (2, 256), (3, 200), (8, 1030)])
+@pytest.mark.parametrize("S,width", [(1, 40), (2, 256), (3, 200), (4, 50), (8, 1030), (12, 96), (16, 33)])
 def test_stream_write_read_and_norm(ops, dtype, S, width):
     g = torch.Generator().manual_seed(S * 1000 + width)
     dt, T, ref = DTYPES[dtype], 19, TorchOps()
